@@ -30,8 +30,9 @@ from .pages import PageAccountingError, PagePool
 class CacheRequirement:
     """What one run of a layer keeps between steps.
 
-    kind "kv": pages of keys and values, ``n_kv_heads`` x ``head_dim`` per token,
-    all of them (``window`` None) or the last ``window``.
+    kind "kv": pages of keys and values, ``n_kv_heads`` x ``head_dim`` per token
+    (values ``v_head_dim`` a head when that is given), all of them (``window`` None)
+    or the last ``window``.
     kind "state": one tensor of ``state_shape``/``state_dtype`` per request.
     kind "none": nothing.
     """
@@ -43,10 +44,15 @@ class CacheRequirement:
     dtype: torch.dtype | None = None
     state_shape: tuple[int, ...] = ()
     state_dtype: torch.dtype | None = None
+    v_head_dim: int | None = None
+
+    @property
+    def value_dim(self) -> int:
+        return self.v_head_dim if self.v_head_dim is not None else self.head_dim
 
     def group_key(self):
         if self.kind == "kv":
-            return ("kv", self.n_kv_heads, self.head_dim, self.window, self.dtype)
+            return ("kv", self.n_kv_heads, self.head_dim, self.value_dim, self.window, self.dtype)
         if self.kind == "state":
             return ("state", self.state_shape, self.state_dtype)
         return ("none",)
@@ -64,7 +70,12 @@ class KVGroup:
     entries: list[int]                       # schedule entries (runs) stored in this group, in order
     pool: PagePool
     k: torch.Tensor | None = None            # [len(entries), n_pages, n_kv_heads, page_size, head_dim]
-    v: torch.Tensor | None = None
+    v: torch.Tensor | None = None            # the same with v_head_dim as its last size
+    v_head_dim: int = 0                      # 0: as head_dim
+
+    @property
+    def value_dim(self) -> int:
+        return self.v_head_dim or self.head_dim
     tables: dict = field(default_factory=dict)      # request id -> list of page ids, -1 where released
     first_live: dict = field(default_factory=dict)  # request id -> first logical page still held
 
@@ -106,7 +117,7 @@ class CacheManager:
                 if key not in keys:
                     keys[key] = len(self.kv_groups)
                     self.kv_groups.append(KVGroup(len(self.kv_groups), req.n_kv_heads, req.head_dim, req.window,
-                                                  req.dtype, [], PagePool(n_pages)))
+                                                  req.dtype, [], PagePool(n_pages), v_head_dim=req.value_dim))
                 g = self.kv_groups[keys[key]]
                 g.entries.append(entry)
                 self.bindings.append(CacheBinding("kv", g.index, len(g.entries) - 1))
@@ -135,17 +146,18 @@ class CacheManager:
     def allocate_storage(self, device) -> None:
         self.device = torch.device(device)
         for g in self.kv_groups:
-            shape = (len(g.entries), self.n_pages, g.n_kv_heads, self.page_size, g.head_dim)
+            shape = (len(g.entries), self.n_pages, g.n_kv_heads, self.page_size)
             fill = float("nan") if self.poison_free_pages else 0.0
-            g.k = torch.full(shape, fill, dtype=g.dtype, device=self.device)
-            g.v = torch.full(shape, fill, dtype=g.dtype, device=self.device)
+            g.k = torch.full(shape + (g.head_dim,), fill, dtype=g.dtype, device=self.device)
+            g.v = torch.full(shape + (g.value_dim,), fill, dtype=g.dtype, device=self.device)
         for g in self.state_groups:
             g.data = torch.zeros((len(g.entries), self.max_requests) + g.shape, dtype=g.dtype, device=self.device)
 
     def storage_bytes(self) -> int:
         n = 0
         for g in self.kv_groups:
-            n += 2 * len(g.entries) * self.n_pages * g.n_kv_heads * self.page_size * g.head_dim * g.dtype.itemsize
+            n += (len(g.entries) * self.n_pages * g.n_kv_heads * self.page_size * (g.head_dim + g.value_dim)
+                  * g.dtype.itemsize)
         for g in self.state_groups:
             per = 1
             for s in g.shape:

@@ -1,3 +1,4 @@
+from .barerax import BareraxConfig
 from .llama import ConfigError, LlamaConfig
 from .registry import (
     ARCHITECTURES,
@@ -12,12 +13,16 @@ from .registry import (
 )
 from .spec import (
     AttentionSpec,
+    BigramDecoderSpec,
     BlockSpec,
     FeedForwardSpec,
     GatedMLPSpec,
+    GeneralDeltaSpec,
+    HeadNormSpec,
     MixerSpec,
     ModelSpec,
     NormSpec,
+    PolyNormMLPSpec,
     PositionSpec,
     RopeScaling,
     ScheduleEntry,

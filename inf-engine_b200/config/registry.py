@@ -24,14 +24,17 @@ from .llama import ConfigError, LlamaConfig
 @dataclass(frozen=True)
 class Architecture:
     name: str
-    parse_config: Callable[[dict], object]   # config.json dict -> typed config with .model_spec()
+    parse_config: Callable[..., object]      # config.json dict -> typed config with .model_spec()
+    reads_shapes: bool = False               # parse_config(d, tensor_shapes): some sizes are tensor shapes only
 
 
 ARCHITECTURES: dict[str, Architecture] = {}
 
 
-def register_architecture(name: str, parse_config: Callable[[dict], object]) -> None:
-    ARCHITECTURES[name] = Architecture(name, parse_config)
+def register_architecture(name: str, parse_config: Callable[..., object], reads_shapes: bool = False) -> None:
+    """``reads_shapes``: the family leaves some sizes to the checkpoint's tensor shapes; ``parse_config`` then takes
+    a second argument, name -> shape of the checkpoint beside ``config.json`` (empty when there is none)."""
+    ARCHITECTURES[name] = Architecture(name, parse_config, reads_shapes)
 
 
 def get_architecture(name: str) -> Architecture:
@@ -43,12 +46,17 @@ def get_architecture(name: str) -> Architecture:
         ) from None
 
 
-def parse_config_dict(d: dict):
+def parse_config_dict(d: dict, tensor_shapes: dict | None = None):
     """Typed configuration of a ``config.json`` dictionary, chosen by its architecture."""
     archs = d.get("architectures")
+    if not archs and isinstance(d.get("architecture"), str):
+        archs = [d["architecture"]]            # some families name theirs with one string
     if not archs:
-        raise ConfigError("config.json has no 'architectures' entry")
-    return get_architecture(str(archs[0])).parse_config(d)
+        raise ConfigError("config.json has no 'architectures' (or 'architecture') entry")
+    arch = get_architecture(str(archs[0]))
+    if arch.reads_shapes:
+        return arch.parse_config(d, tensor_shapes or {})
+    return arch.parse_config(d)
 
 
 def detect_config(model_dir: str | Path):
@@ -57,7 +65,16 @@ def detect_config(model_dir: str | Path):
     if not path.is_file():
         raise FileNotFoundError(f"no config.json in {model_dir}")
     with open(path) as f:
-        return parse_config_dict(json.load(f))
+        d = json.load(f)
+    shapes = None
+    archs = d.get("architectures") or [d.get("architecture")]
+    if archs[0] in ARCHITECTURES and ARCHITECTURES[archs[0]].reads_shapes:
+        from ..weights.safetensors_io import open_checkpoint     # headers only; no tensor is read
+        try:
+            shapes = {n: tuple(t.shape) for n, t in open_checkpoint(model_dir).items()}
+        except FileNotFoundError:
+            shapes = None
+    return parse_config_dict(d, shapes)
 
 
 _PRESET_DIR = Path(__file__).resolve().parent / "presets"
@@ -81,3 +98,11 @@ def get_preset(name: str):
 get_llama_config = get_preset
 
 register_architecture("LlamaForCausalLM", LlamaConfig.from_hf_dict)
+
+
+def _barerax(d: dict, tensor_shapes: dict | None = None):
+    from .barerax import BareraxConfig
+    return BareraxConfig.from_dict(d, tensor_shapes)
+
+
+register_architecture("Barerax", _barerax, reads_shapes=True)

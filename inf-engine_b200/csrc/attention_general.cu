@@ -1,5 +1,5 @@
 // Paged causal attention for any mix of prompt portions and decode tokens, any
-// head size that is a multiple of 16 up to 256, any number of heads and groups,
+// head size up to 256 (values: a multiple of 8), any number of heads and groups,
 // an optional window.  float32 arithmetic on CUDA cores with float32 or
 // bfloat16 storage: this is the kernel of the true 32-bit path and the fallback
 // of the bfloat16 path for sizes that the tensor-core kernels do not take.
@@ -12,7 +12,10 @@
 // there before this kernel runs, so every cut of the work sees the same keys.
 // An optional additive term enters the score before the softmax: a float32 table
 // bias[head][distance], distance = p - j clamped to the table's last column
-// (position encodings that bias scores by how far back a key lies).
+// (position encodings that bias scores by how far back a key lies).  An optional
+// float32 multiplier per query head scales the score before that term is added
+// (a learned temperature of each head), and values may have another head size
+// than queries and keys (hd_v; the pools are laid out with their own sizes).
 //
 // Work split: a block takes one (request, kv head) and a tile of 32
 // (token, head-in-group) pairs, so the `group` query heads that share a kv head
@@ -42,6 +45,8 @@ struct AttnGeneralParams {
   float scale;
   const float* score_bias;  // [n_heads][bias_dists] or null
   int bias_dists;
+  const float* head_scale;  // [n_heads] or null: the score is scale * head_scale[head] * (q . k)
+  int hd_v;                 // head size of the values and of the output
 };
 
 template <typename T>
@@ -49,12 +54,12 @@ __global__ void __launch_bounds__(AG_THREADS) attention_general_kernel(AttnGener
   extern __shared__ float smem[];
   pdl_trigger();
   pdl_wait();
-  const int hd = p.hd;
+  const int hd = p.hd, hdv = p.hd_v;
   const int ldq = hd + 1;
   float* Qs = smem;                      // [ROWS][hd+1]
   float* Ks = Qs + AG_ROWS * ldq;        // [KEYS][hd+1]
   float* Vs = Ks + AG_KEYS * ldq;        // [KEYS][hd]
-  float* Ps = Vs + AG_KEYS * hd;         // [ROWS][KEYS+1]
+  float* Ps = Vs + AG_KEYS * hdv;        // [ROWS][KEYS+1]  (Vs is [KEYS][hdv])
 
   const int w = blockIdx.x;
   const int c = blockIdx.y;              // kv head
@@ -91,9 +96,9 @@ __global__ void __launch_bounds__(AG_THREADS) attention_general_kernel(AttnGener
   const int my_t = row_valid ? my_pair / group : 0;
   const int my_limit = ctx + my_t;                                    // last visible key
   const int my_first = p.window > 0 ? max(0, my_limit - p.window + 1) : 0;
-  const float* my_bias = (p.score_bias != nullptr && row_valid)
-                             ? p.score_bias + (size_t)(c * group + (my_pair - my_t * group)) * p.bias_dists
-                             : nullptr;
+  const int my_head = c * group + (row_valid ? my_pair - my_t * group : 0);
+  const float* my_bias = (p.score_bias != nullptr && row_valid) ? p.score_bias + (size_t)my_head * p.bias_dists : nullptr;
+  const float my_scale = p.head_scale != nullptr ? p.scale * p.head_scale[my_head] : p.scale;
 
   const int last_pair = min(pair0 + AG_ROWS, n_pairs) - 1;
   const int key_end = ctx + last_pair / group + 1;                     // keys [.., key_end) matter to the tile
@@ -108,24 +113,31 @@ __global__ void __launch_bounds__(AG_THREADS) attention_general_kernel(AttnGener
 #pragma unroll
   for (int i = 0; i < AG_MAX_ACC; ++i) acc[i] = 0.f;
   float m_run = -INFINITY, l_run = 0.f;
-  const int n_acc = hd >> 3;
+  const int n_acc = hdv >> 3;
 
   for (int kt = key_begin; kt < key_end; kt += AG_KEYS) {
     __syncthreads();  // previous tile fully consumed (and Qs staged, first time)
     for (int idx = tid; idx < AG_KEYS * hd; idx += AG_THREADS) {
       const int kk = idx / hd, d = idx - kk * hd;
       const int kp = kt + kk;
-      float kv = 0.f, vv = 0.f;
+      float kv = 0.f;
       if (kp < key_end) {
         const int page = IE_PAGE(table[kp / p.page_size]);
-        if (page >= 0) {
-          const size_t a = (((size_t)page * p.n_kv_heads + c) * p.page_size + (kp % p.page_size)) * hd + d;
-          kv = to_f32(kpool[a]);
-          vv = to_f32(vpool[a]);
-        }
+        if (page >= 0)
+          kv = to_f32(kpool[(((size_t)page * p.n_kv_heads + c) * p.page_size + (kp % p.page_size)) * hd + d]);
       }
       Ks[kk * ldq + d] = kv;
-      Vs[kk * hd + d] = vv;
+    }
+    for (int idx = tid; idx < AG_KEYS * hdv; idx += AG_THREADS) {
+      const int kk = idx / hdv, d = idx - kk * hdv;
+      const int kp = kt + kk;
+      float vv = 0.f;
+      if (kp < key_end) {
+        const int page = IE_PAGE(table[kp / p.page_size]);
+        if (page >= 0)
+          vv = to_f32(vpool[(((size_t)page * p.n_kv_heads + c) * p.page_size + (kp % p.page_size)) * hdv + d]);
+      }
+      Vs[kk * hdv + d] = vv;
     }
     __syncthreads();
 
@@ -141,7 +153,7 @@ __global__ void __launch_bounds__(AG_THREADS) attention_general_kernel(AttnGener
       const float* kr = Ks + kk * ldq;
       for (int d = 0; d < hd; ++d) dot += qr[d] * kr[d];
       const bool visible = row_valid && kp <= my_limit && kp >= my_first;
-      float sc = dot * p.scale;
+      float sc = dot * my_scale;
       if (visible && my_bias != nullptr) sc += my_bias[min(my_limit - kp, p.bias_dists - 1)];
       s[jj] = visible ? sc : -INFINITY;
       tile_max = fmaxf(tile_max, s[jj]);
@@ -176,7 +188,7 @@ __global__ void __launch_bounds__(AG_THREADS) attention_general_kernel(AttnGener
         float a = acc[i] * alpha;
         const float* vcol = Vs + sub + 8 * i;
 #pragma unroll 8
-        for (int kk = 0; kk < AG_KEYS; ++kk) a += pr_[kk] * vcol[kk * hd];
+        for (int kk = 0; kk < AG_KEYS; ++kk) a += pr_[kk] * vcol[kk * hdv];
         acc[i] = a;
       }
     }
@@ -184,7 +196,7 @@ __global__ void __launch_bounds__(AG_THREADS) attention_general_kernel(AttnGener
 
   if (row_valid) {
     const int j = my_pair - my_t * group;
-    T* o = (T*)p.out + (size_t)(q0 + my_t) * p.out_stride + (c * group + j) * hd;
+    T* o = (T*)p.out + (size_t)(q0 + my_t) * p.out_stride + (c * group + j) * hdv;
     const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
 #pragma unroll
     for (int i = 0; i < AG_MAX_ACC; ++i)
@@ -197,9 +209,10 @@ extern "C" int ie_attention_general(const void* q, void* out, const void* kpool,
                                     const int* work_req, const int* work_pair0, int q_stride, int out_stride,
                                     int table_stride, int n_work, int n_heads, int n_kv_heads, int hd,
                                     int page_size, int window, float scale, int act_dtype, const float* score_bias,
-                                    int bias_dists, cudaStream_t stream) {
+                                    int bias_dists, const float* head_scale, int hd_v, cudaStream_t stream) {
   if (n_work <= 0) return IE_OK;
-  if (hd % 16 || hd > 8 * AG_MAX_ACC || hd <= 0) return IE_BAD_SIZE;
+  if (hd_v <= 0) hd_v = hd;
+  if (hd <= 0 || hd > 8 * AG_MAX_ACC || hd_v % 8 || hd_v > 8 * AG_MAX_ACC) return IE_BAD_SIZE;
   if (n_kv_heads <= 0 || n_heads % n_kv_heads) return IE_BAD_SIZE;
   if (score_bias != nullptr && bias_dists <= 0) return IE_BAD_SIZE;
   AttnGeneralParams p;
@@ -208,8 +221,9 @@ extern "C" int ie_attention_general(const void* q, void* out, const void* kpool,
   p.q_stride = q_stride; p.out_stride = out_stride; p.table_stride = table_stride;
   p.n_work = n_work; p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.hd = hd; p.page_size = page_size;
   p.window = window; p.scale = scale; p.score_bias = score_bias; p.bias_dists = bias_dists;
+  p.head_scale = head_scale; p.hd_v = hd_v;
   const size_t smem = sizeof(float) * ((size_t)AG_ROWS * (hd + 1) + (size_t)AG_KEYS * (hd + 1) +
-                                       (size_t)AG_KEYS * hd + (size_t)AG_ROWS * (AG_KEYS + 1));
+                                       (size_t)AG_KEYS * hd_v + (size_t)AG_ROWS * (AG_KEYS + 1));
   dim3 grid(n_work, n_kv_heads);
   cudaError_t e;
   if (act_dtype == IE_F32) {

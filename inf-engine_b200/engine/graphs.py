@@ -139,6 +139,7 @@ class DecodeGraphs:
         h[o["token_ids"][0]:o["token_ids"][0] + R] = [e.tokens[0] for e in entries]
         h[o["positions"][0]:o["positions"][0] + R] = lens
         h[o["ctx_before"][0]:o["ctx_before"][0] + R] = lens
+        h[o["slots"][0]:o["slots"][0] + B] = -1               # padding rows have no state slot
         h[o["slots"][0]:o["slots"][0] + R] = [cache.slots[e.rid] for e in entries]
         for g, w in enumerate(b.widths):
             grp = cache.kv_groups[g]
@@ -196,8 +197,11 @@ class DecodeGraphs:
         saved = rt.ws
         rt.ws = self.ws
         try:
+            ran = False
             if b.graph is None or b.generation != self.generation:
-                # warm-up outside capture (sizes the buffers, builds the work lists), then capture
+                # One pass outside capture sizes the buffers and builds the work lists; it is also this step's real
+                # run: a model with state per request (a recurrent mixer, the last token of a sequence) must see
+                # every token once, so the graph captured after it is first replayed by the NEXT step it serves.
                 before = self.ws.moves
                 cs = self._capture_stream
                 if cs is None:
@@ -236,10 +240,12 @@ class DecodeGraphs:
                 b.n_kernels = kernels.LAUNCHES - n0
                 b.graph, b.generation = g, self.generation
                 self.captures += 1
+                ran = True
             from .. import kernels
-            b.graph.replay()                      # capture recorded the launches; this runs them
-            kernels.LAUNCHES += b.n_kernels
-            self.replays += 1
+            if not ran:
+                b.graph.replay()                  # capture recorded the launches; this runs them
+                kernels.LAUNCHES += b.n_kernels
+                self.replays += 1
         finally:
             rt.ws = saved
         return b.logits[:R], (b.sampled[:R] if sample_rows is not None else None)

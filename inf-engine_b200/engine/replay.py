@@ -14,7 +14,8 @@ float32 logits at the wanted places, in the order of the entries and of
 every step the line ``done <step>`` is printed and flushed.  ``end`` lists
 requests whose pages and slot are given back after the step.  The page pool is
 made for ``--max-tokens`` tokens (each live request's count rounded up to the
-page size), so pages are used again.
+page size) and there are state slots for ``--max-requests`` live requests (four
+unless told otherwise), so pages and slots are used again.
 """
 
 from __future__ import annotations
@@ -24,7 +25,7 @@ import json
 import sys
 from pathlib import Path
 
-MAX_LIVE_REQUESTS = 64
+MAX_LIVE_REQUESTS = 4
 
 
 def main(argv=None) -> int:
@@ -35,6 +36,8 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens that live requests hold at any time (rounded up per request to 64)")
     ap.add_argument("--page-size", type=int, default=16, help="tokens per cache page (a divisor of 64)")
+    ap.add_argument("--max-requests", type=int, default=MAX_LIVE_REQUESTS,
+                    help="state slots: the most requests that are live at any time")
     ap.add_argument("--poison-free-pages", action="store_true",
                     help="fill every cache page that no request holds with NaN (at the start and when it is given back)")
     ap.add_argument("--device", default="cuda:0")
@@ -55,7 +58,7 @@ def main(argv=None) -> int:
     out_dir.mkdir(parents=True, exist_ok=True)
     n_pages = max(1, -(-args.max_tokens // args.page_size))
     runner = ModelRunner.from_dir(args.model, dtype=args.dtype, device=args.device, page_size=args.page_size,
-                                  n_pages=n_pages, max_requests=MAX_LIVE_REQUESTS,
+                                  n_pages=n_pages, max_requests=args.max_requests,
                                   poison_free_pages=args.poison_free_pages)
     for line in sys.stdin:
         line = line.strip()
@@ -68,7 +71,7 @@ def main(argv=None) -> int:
             rid = e["id"]
             if not runner.is_open(rid):
                 if not runner.open(rid):
-                    raise RuntimeError(f"step {step}: more than {MAX_LIVE_REQUESTS} live requests")
+                    raise RuntimeError(f"step {step}: more than {args.max_requests} live requests")
             entries.append(StepEntry(rid, [int(t) for t in e["tokens"]], [int(w) for w in e.get("want", [])]))
         logits = runner.step(entries)
         if logits is not None:

@@ -80,13 +80,21 @@ def core():
         lib.ie_residual_add.argtypes = [P, P, I, I, I, P]
         lib.ie_rope_kv_write.argtypes = [P, P, P, I, I, P, P, P, P, P, P, I, I, I, I, I, I, I, P]
         lib.ie_silu_mul.argtypes = [P, P, I, I, I, I, I, P]
-        lib.ie_attention_general.argtypes = [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, I, P]
+        lib.ie_attention_general.argtypes = [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, I, P, I, P]
+        lib.ie_layernorm.argtypes = [P, P, P, P, I, P, I, P, I, I, F, P]
+        lib.ie_embed_bigram.argtypes = [P, P, P, P, I, P, P, I, P, P, I, I, I, I, L, L, P]
+        lib.ie_add_bias.argtypes = [P, I, P, I, I, I, I, P]
+        lib.ie_tanh.argtypes = [P, P, I, I, I, I, P]
+        lib.ie_polynorm.argtypes = [P, P, P, I, P, I, I, I, I, F, P]
+        lib.ie_headnorm_kv_write.argtypes = [P, P, P, I, I, I, P, P, I, F, P, P, P, I, I, I, I, I, I, I, I, P]
         lib.ie_gemm_simt.argtypes = [P, I, P, I, P, I, I, I, I, I, I, I, P]
         lib.ie_argmax.argtypes = [P, P, I, I, L, P]
         lib.ie_repetition_penalty.argtypes = [P, P, P, I, I, L, I, P]
         lib.ie_sample.argtypes = [P, P, P, I, I, L, P]
         for name in ("ie_embed_gather", "ie_rmsnorm", "ie_residual_add", "ie_rope_kv_write", "ie_silu_mul",
-                     "ie_attention_general", "ie_gemm_simt", "ie_argmax", "ie_repetition_penalty", "ie_sample"):
+                     "ie_attention_general", "ie_gemm_simt", "ie_argmax", "ie_repetition_penalty", "ie_sample",
+                     "ie_layernorm", "ie_embed_bigram", "ie_add_bias", "ie_tanh", "ie_polynorm",
+                     "ie_headnorm_kv_write"):
             getattr(lib, name).restype = c_int
         _core = lib
         _apply_check_limits()
@@ -100,6 +108,21 @@ def embed_gather(ids: torch.Tensor, table: torch.Tensor, residual: torch.Tensor)
     n, d = residual.shape
     _check(core().ie_embed_gather(_ptr(ids), _ptr(table), dtype_code(table.dtype), _ptr(residual), n, d,
                                   table.shape[0], _stream()), "embed_gather")
+
+
+def embed_bigram(ids: torch.Tensor, positions: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor,
+                 n_requests: int, table: torch.Tensor, bigram: torch.Tensor, prev_state: torch.Tensor,
+                 residual: torch.Tensor, buckets: int, mul_prev: int, mul_cur: int) -> None:
+    """residual[n] = table[ids[n]] + bigram[row] as float32, row = (previous token * mul_prev + ids[n] * mul_cur) mod
+    buckets, or ``buckets`` (the last row) at position 0.  ``prev_state`` (int32, one word per request slot) holds the
+    last token of every request between steps; this call reads and updates it."""
+    assert ids.dtype == positions.dtype == q_start.dtype == slots.dtype == prev_state.dtype == torch.int32
+    assert residual.dtype == torch.float32 and table.is_contiguous() and bigram.is_contiguous()
+    assert table.dtype == bigram.dtype and bigram.shape == (buckets + 1, table.shape[1]) and prev_state.is_contiguous()
+    n, d = residual.shape
+    _check(core().ie_embed_bigram(_ptr(ids), _ptr(positions), _ptr(q_start), _ptr(slots), n_requests, _ptr(table),
+                                  _ptr(bigram), dtype_code(table.dtype), _ptr(prev_state), _ptr(residual), n, d,
+                                  table.shape[0], int(buckets), int(mul_prev), int(mul_cur), _stream()), "embed_bigram")
 
 
 def patch_tokens(ids: torch.Tensor, src: torch.Tensor, prev: torch.Tensor) -> None:
@@ -127,6 +150,64 @@ def rmsnorm(residual: torch.Tensor, delta: torch.Tensor | None, gain: torch.Tens
     assert gain.shape == (d,) and out.shape[1] == d
     _check(core().ie_rmsnorm(_ptr(residual), _ptr(delta), _ptr(gain), dtype_code(gain.dtype), _ptr(out),
                              dtype_code(out.dtype), _ptr(row_index), n_rows, d, float(eps), _stream()), "rmsnorm")
+
+
+def layernorm(residual: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, bias: torch.Tensor | None,
+              out: torch.Tensor, eps: float, row_index: torch.Tensor | None = None) -> None:
+    """out = (x - mean) / sqrt(var + eps) * weight + bias with x = residual (+ delta); residual takes the sum unless
+    rows are gathered."""
+    d = residual.shape[-1]
+    n_rows = out.shape[0]
+    assert residual.dtype == torch.float32 and residual.is_contiguous() and out.is_contiguous()
+    assert delta is None or (delta.dtype == out.dtype and delta.is_contiguous() and delta.shape == residual.shape)
+    assert weight.shape == (d,) and out.shape[1] == d and (bias is None or (bias.shape == (d,) and bias.dtype == weight.dtype))
+    _check(core().ie_layernorm(_ptr(residual), _ptr(delta), _ptr(weight), _ptr(bias), dtype_code(weight.dtype),
+                               _ptr(out), dtype_code(out.dtype), _ptr(row_index), n_rows, d, float(eps), _stream()),
+           "layernorm")
+
+
+def add_bias(out: torch.Tensor, bias: torch.Tensor) -> None:
+    """out[n, :] += bias (out may be a column slice)."""
+    n, cols = out.shape
+    assert out.stride(1) == 1 and bias.shape == (cols,) and bias.is_contiguous()
+    _check(core().ie_add_bias(_ptr(out), dtype_code(out.dtype), _ptr(bias), dtype_code(bias.dtype), n, cols,
+                              out.stride(0), _stream()), "add_bias")
+
+
+def tanh(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out = tanh(x); x may be a column slice, out is contiguous."""
+    n, cols = x.shape
+    assert x.stride(1) == 1 and out.is_contiguous() and out.shape == x.shape and out.dtype == x.dtype
+    _check(core().ie_tanh(_ptr(x), _ptr(out), n, cols, x.stride(0), dtype_code(x.dtype), _stream()), "tanh")
+
+
+def polynorm(z: torch.Tensor, bias: torch.Tensor | None, coef: torch.Tensor, out: torch.Tensor, eps: float) -> None:
+    """out = c0 N(y) + c1 N(y^2) + c2 N(y^3) + c3 with y = z (+ bias) and N(x) = x / sqrt(mean(x^2) + eps) over a row;
+    ``coef`` holds the four numbers on the device."""
+    n, cols = z.shape
+    assert z.stride(1) == 1 and out.is_contiguous() and out.shape == z.shape and out.dtype == z.dtype
+    assert coef.shape == (4,) and (bias is None or (bias.shape == (cols,) and bias.dtype == coef.dtype))
+    _check(core().ie_polynorm(_ptr(z), _ptr(bias), _ptr(coef), dtype_code(coef.dtype), _ptr(out), dtype_code(out.dtype),
+                              n, cols, z.stride(0), float(eps), _stream()), "polynorm")
+
+
+def headnorm_kv_write(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_gain: torch.Tensor | None,
+                      k_gain: torch.Tensor | None, eps: float, slot_mapping: torch.Tensor | None,
+                      kpool: torch.Tensor | None, vpool: torch.Tensor | None, n_heads: int, n_kv_heads: int,
+                      head_dim: int, v_head_dim: int, page_size: int) -> None:
+    """RMS norm of every query head (in place) and key head with gains of the head's size shared by all heads
+    (None: no norm on that side); the normalised keys and the raw values go to their page slots (if pools are given).
+    q, k, v are row-strided views [n, heads * head size]; values have ``v_head_dim`` elements a head."""
+    n = q.shape[0]
+    assert q.stride(1) == 1 and k.stride(1) == 1 and v.stride(1) == 1
+    gain = q_gain if q_gain is not None else k_gain
+    assert q_gain is None or k_gain is None or q_gain.dtype == k_gain.dtype
+    write = kpool is not None
+    _check(core().ie_headnorm_kv_write(_ptr(q), _ptr(k), _ptr(v), q.stride(0), k.stride(0), v.stride(0), _ptr(q_gain),
+                                       _ptr(k_gain), dtype_code(gain.dtype) if gain is not None else IE_F32, float(eps),
+                                       _ptr(slot_mapping), _ptr(kpool), _ptr(vpool), n, n_heads, n_kv_heads, head_dim,
+                                       v_head_dim, page_size, 1 if write else 0, dtype_code(q.dtype), _stream()),
+           "headnorm_kv_write")
 
 
 def residual_add(residual: torch.Tensor, delta: torch.Tensor) -> None:
@@ -167,19 +248,25 @@ def attention_general(q: torch.Tensor, out: torch.Tensor, kpool: torch.Tensor, v
                       block_table: torch.Tensor, q_start: torch.Tensor, ctx_before: torch.Tensor,
                       work_req: torch.Tensor, work_pair0: torch.Tensor, n_work: int, n_heads: int,
                       n_kv_heads: int, head_dim: int, page_size: int, window: int | None, scale: float,
-                      score_bias: torch.Tensor | None = None) -> None:
+                      score_bias: torch.Tensor | None = None, head_scale: torch.Tensor | None = None,
+                      v_head_dim: int | None = None) -> None:
     """Paged causal attention in float32 arithmetic.  ``score_bias`` (float32 [n_heads, D], contiguous) is added to
-    the scaled score of a query at position p and a key at position j as ``score_bias[head, min(p - j, D - 1)]``."""
+    the scaled score of a query at position p and a key at position j as ``score_bias[head, min(p - j, D - 1)]``.
+    ``head_scale`` (float32 [n_heads]) multiplies the score of its head beside ``scale``.  ``v_head_dim``: head size of
+    the values and of ``out`` when it is not ``head_dim``."""
     assert q.stride(1) == 1 and out.stride(1) == 1 and kpool.dtype == q.dtype == out.dtype
     assert block_table.dtype == torch.int32 and block_table.stride(1) == 1
     if score_bias is not None:
         assert score_bias.dtype is torch.float32 and score_bias.is_contiguous() and score_bias.shape[0] == n_heads
+    if head_scale is not None:
+        assert head_scale.dtype is torch.float32 and head_scale.is_contiguous() and head_scale.shape == (n_heads,)
     _check(core().ie_attention_general(_ptr(q), _ptr(out), _ptr(kpool), _ptr(vpool), _ptr(block_table),
                                        _ptr(q_start), _ptr(ctx_before), _ptr(work_req), _ptr(work_pair0),
                                        q.stride(0), out.stride(0), block_table.stride(0), n_work, n_heads,
                                        n_kv_heads, head_dim, page_size, int(window or 0), float(scale),
                                        dtype_code(q.dtype), _ptr(score_bias),
-                                       score_bias.shape[1] if score_bias is not None else 0, _stream()),
+                                       score_bias.shape[1] if score_bias is not None else 0, _ptr(head_scale),
+                                       int(v_head_dim or head_dim), _stream()),
            f"attention_general(head_dim={head_dim}, heads={n_heads}/{n_kv_heads})")
 
 
@@ -311,6 +398,50 @@ def attention_decode_fused(q, k_new, v_new, out, kpool, vpool, block_table, q_st
                                          n_kv_heads, head_dim, page_size, int(window or 0), float(scale),
                                          1 if write_kv else 0, n_splits, split_keys, _stream()),
            "attention_decode_fused")
+
+
+# ------------------------------------------------- generalized delta rule (a recurrent mixer)
+DELTA_RULE_MAX_DIM = 128
+_delta: dict[int, object] = {}
+
+
+def delta_rule_library(head_dim: int):
+    """The delta-rule kernel built for one head size; compiled when first asked for."""
+    if not 1 <= head_dim <= DELTA_RULE_MAX_DIM:
+        raise KernelError(f"the delta-rule kernel keeps a state column in registers: head sizes up to "
+                          f"{DELTA_RULE_MAX_DIM}, not {head_dim}")
+    lib = _delta.get(head_dim)
+    if lib is None:
+        defines = {"IE_DR_DIM": head_dim, **BUILD_DEFINES.get("delta_rule", {})}
+        lib = load_library(f"delta_rule_d{head_dim}", ["delta_rule.cu"], defines)
+        P, I, F = c_void_p, c_int, c_float
+        lib.ie_delta_rule.argtypes = [P, P, P, P, P, I, P, I, P, P, P, I, P, P, I, P, P, I, I, I, F, F, F, I, I, P]
+        lib.ie_delta_rule.restype = c_int
+        _delta[head_dim] = lib
+        _apply_check_limits()
+    return lib
+
+
+def delta_rule(r, k, v, a_pre, g, w_pre, a_bias, w_bias, out_gain, state, out, q_start, slots, n_requests: int,
+               n_heads: int, head_dim: int, decay_rate: float, key_eps: float, norm_eps: float,
+               write_state: bool = True) -> None:
+    """One step of the generalized delta rule for every (request, head) of the batch.
+
+    ``r, k, v, a_pre, g``: [n, heads * head_dim] views with one row stride (columns of one projection buffer) in the
+    activation type; ``w_pre`` float32 [n, heads * head_dim]; ``a_bias, w_bias, out_gain`` [heads * head_dim];
+    ``state`` float32 [slots, heads, head_dim, head_dim], read and (with ``write_state``) written at ``slots[request]``;
+    ``out`` [n, heads * head_dim] in the activation type: the normed, gated result for the output projection."""
+    width = n_heads * head_dim
+    for t in (r, k, v, a_pre, g):
+        assert t.dtype == r.dtype and t.stride(1) == 1 and t.stride(0) == r.stride(0) and t.shape[1] == width
+    assert w_pre.dtype is torch.float32 and w_pre.stride(1) == 1 and state.dtype is torch.float32 and state.is_contiguous()
+    assert a_bias.dtype == w_bias.dtype == out_gain.dtype and out.dtype == r.dtype and out.stride(1) == 1
+    assert state.shape[1:] == (n_heads, head_dim, head_dim)
+    _check(delta_rule_library(head_dim).ie_delta_rule(
+        _ptr(r), _ptr(k), _ptr(v), _ptr(a_pre), _ptr(g), r.stride(0), _ptr(w_pre), w_pre.stride(0), _ptr(a_bias),
+        _ptr(w_bias), _ptr(out_gain), dtype_code(a_bias.dtype), _ptr(state), _ptr(out), out.stride(0), _ptr(q_start),
+        _ptr(slots), n_requests, n_heads, head_dim, float(decay_rate), float(key_eps), float(norm_eps),
+        1 if write_state else 0, dtype_code(r.dtype), _stream()), f"delta_rule(head_dim={head_dim}, heads={n_heads})")
 
 
 # ----------------------------------------------- weight-streaming product for few rows
@@ -509,8 +640,8 @@ def attention_tcgen05(q, out, kpool, vpool, block_table, q_start, ctx_before, wo
 
 # ------------------------------------------------ a checks build: page ids, slots and token ids compared with limits
 # (the device has no sanitizer here: this is what stands in for one while debugging a cache manager or a new part)
-CHECK_LIBRARIES = ("core", "attn_mma", "attn_tcgen05")
-CHECK_UNITS = ("elementwise", "attention_general", "attention_mma", "attention_tcgen05")
+CHECK_LIBRARIES = ("core", "attn_mma", "attn_tcgen05", "delta_rule")
+CHECK_UNITS = ("elementwise", "rowwise", "attention_general", "attention_mma", "attention_tcgen05", "delta_rule")
 CHECK_CODES = {1: "page id", 2: "cache slot", 3: "token id"}
 _check_limits: tuple[int, int, int] | None = None
 

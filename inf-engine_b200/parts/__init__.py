@@ -1,11 +1,12 @@
-from . import attention, block, feedforward, model, norms, positions  # noqa: F401  (register the built-in parts)
+from . import attention, block, delta_rule, feedforward, model, norms, positions  # noqa: F401  (register the built-in parts)
 from .attention import CacheView, PagedAttention
 from .block import PreNormBlock
-from .feedforward import GatedMLP
+from .delta_rule import GeneralDeltaMixer
+from .feedforward import GatedMLP, PolyNormMLP
 from .linear import Linear
-from .model import DecoderModel
-from .norms import RMSNorm
-from .positions import NoPosition, Rotary, rotary_inv_freq, rotary_tables
+from .model import BigramDecoderModel, DecoderModel
+from .norms import LayerNorm, RMSNorm
+from .positions import BucketedBias, NoPosition, Rotary, distance_bucket, rotary_inv_freq, rotary_tables
 from .registry import (
     BLOCKS,
     FEEDFORWARDS,

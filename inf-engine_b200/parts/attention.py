@@ -7,7 +7,14 @@ tokens; the attention kernel then reads every key and value through the block
 table, so a prompt portion, a decode token and a whole prompt take the same
 path.  kv head c serves query heads c*g .. c*g+g-1 (:27-44) inside the kernel;
 nothing is expanded in memory.  Scores are scaled by head_dim**-0.5 (the
-library default the reference relies on, :123-137).
+library default the reference relies on, :123-137) unless the spec names a scale.
+
+Options of the spec beyond that: an RMS norm of every query and key head before
+the scores (``qk_norm``, fused with the cache write), a learned multiplier of
+each head's scores (``head_scale``), a bias by distance from the position
+encoding, and values of another head size than queries and keys
+(``v_head_dim``).  A layer that uses one of them runs the general kernel, which
+computes scores and weights in float32; the tensor-core kernels take none.
 """
 
 from __future__ import annotations
@@ -44,17 +51,24 @@ class PagedAttention:
         out = {
             spec.q_proj: ExpectedTensor((spec.n_heads * spec.head_dim, spec.hidden)),
             spec.k_proj: ExpectedTensor((spec.n_kv_heads * spec.head_dim, spec.hidden)),
-            spec.v_proj: ExpectedTensor((spec.n_kv_heads * spec.head_dim, spec.hidden)),
-            spec.o_proj: ExpectedTensor((spec.hidden, spec.n_heads * spec.head_dim)),
+            spec.v_proj: ExpectedTensor((spec.n_kv_heads * spec.value_dim, spec.hidden)),
         }
+        if spec.qk_norm is not None:
+            for name in (spec.qk_norm.q_weight, spec.qk_norm.k_weight):
+                if name is not None:
+                    out[name] = ExpectedTensor((spec.head_dim,), init="gain")
         out.update(position_class(spec.position).expected_tensors(spec.position))
+        if spec.head_scale is not None:
+            out[spec.head_scale] = ExpectedTensor((spec.n_heads,), init="gain")
+        out[spec.o_proj] = ExpectedTensor((spec.hidden, spec.n_heads * spec.value_dim))
         return out
 
     def __init__(self, spec, tensors, rt):
         if spec.n_heads % spec.n_kv_heads:
             raise ValueError(f"{spec.n_heads} query heads are not a multiple of {spec.n_kv_heads} kv heads")
-        if spec.head_dim % 16 or spec.head_dim > 256:
-            raise ValueError(f"attention kernels take head sizes in steps of 16 up to 256, not {spec.head_dim}")
+        if spec.head_dim > 256 or spec.value_dim % 8 or spec.value_dim > 256:
+            raise ValueError(f"attention kernels take head sizes up to 256 (values: in steps of 8), not "
+                             f"{spec.head_dim} and {spec.value_dim}")
         if spec.window is not None and spec.window <= 0:
             raise ValueError("an attention window must be positive")
         self.spec = spec
@@ -64,14 +78,26 @@ class PagedAttention:
         self.qkv = Linear(torch.cat([w.to(dtype) for w in ws], dim=0).contiguous(), rt, "qkv")
         self.o = Linear(tensors[spec.o_proj], rt, "o")
         self.position = build_position(spec.position, tensors, rt)
-        self.scale = float(spec.head_dim) ** -0.5
+        self.scale = float(spec.scale) if spec.scale is not None else float(spec.head_dim) ** -0.5
+        self.v_dim = spec.value_dim
         self.q_width = spec.n_heads * spec.head_dim
-        self.kv_width = spec.n_kv_heads * spec.head_dim
+        self.k_width = spec.n_kv_heads * spec.head_dim
+        self.v_width = spec.n_kv_heads * self.v_dim
+        self.out_width = spec.n_heads * self.v_dim
+        self.kv_width = self.k_width            # where keys and values have one size
+        qn = spec.qk_norm
+        self.q_gain = tensors[qn.q_weight] if qn is not None and qn.q_weight is not None else None
+        self.k_gain = tensors[qn.k_weight] if qn is not None and qn.k_weight is not None else None
+        if self.q_gain is not None and self.k_gain is not None and self.q_gain.dtype != self.k_gain.dtype:
+            self.q_gain, self.k_gain = self.q_gain.float(), self.k_gain.float()
+        self.head_scale = tensors[spec.head_scale].float().contiguous() if spec.head_scale is not None else None
+        # the tensor-core kernels and the fused decode kernel know none of these; such a layer runs the general kernel
+        self.plain = qn is None and self.head_scale is None and self.v_dim == spec.head_dim
 
     def cache_requirement(self) -> CacheRequirement:
         s = self.spec
         return CacheRequirement(kind="kv", n_kv_heads=s.n_kv_heads, head_dim=s.head_dim, window=s.window,
-                                dtype=self.rt.act_dtype)
+                                dtype=self.rt.act_dtype, v_head_dim=None if self.v_dim == s.head_dim else self.v_dim)
 
     def can_fuse(self, n_tokens: int, norm) -> bool:
         return hasattr(norm, "fusable_rms") and self.qkv.streams(n_tokens, normed=True) and self.o.streams(n_tokens)
@@ -81,7 +107,7 @@ class PagedAttention:
         residual sum in the output product's epilogue."""
         rt = self.rt
         n = residual.shape[0]
-        qkv = rt.ws.take("attn_qkv", (n, self.q_width + 2 * self.kv_width), rt.act_dtype)
+        qkv = rt.ws.take("attn_qkv", (n, self.q_width + self.k_width + self.v_width), rt.act_dtype)
         stream_normed(self.qkv, residual, qkv, n, "bf16", norm, ctx)
         out = self._rotate_write_attend(qkv, ctx, cache)
         stream_into_residual(self.o, out, residual, n, ctx, rt)
@@ -89,7 +115,7 @@ class PagedAttention:
     def forward(self, x: torch.Tensor, ctx, cache: CacheView) -> torch.Tensor:
         s, rt = self.spec, self.rt
         n = x.shape[0]
-        qkv = self.qkv(x, rt.ws.take("attn_qkv", (n, self.q_width + 2 * self.kv_width), rt.act_dtype))
+        qkv = self.qkv(x, rt.ws.take("attn_qkv", (n, self.q_width + self.k_width + self.v_width), rt.act_dtype))
         out = self._rotate_write_attend(qkv, ctx, cache)
         return self.o(out, rt.ws.take("mixer_out", (n, s.hidden), rt.act_dtype))
 
@@ -97,14 +123,16 @@ class PagedAttention:
         s, rt = self.spec, self.rt
         n = qkv.shape[0]
         q = qkv[:, :self.q_width]
-        k = qkv[:, self.q_width:self.q_width + self.kv_width]
-        v = qkv[:, self.q_width + self.kv_width:]
+        k = qkv[:, self.q_width:self.q_width + self.k_width]
+        v = qkv[:, self.q_width + self.k_width:]
         kvctx = ctx.kv[cache.group]
         tables = self.position.rotary_tables()
         # a position encoding may bias the scores by distance (float32 [n_heads, D]); only the general kernel takes it
         bias_of = getattr(self.position, "score_bias", None)
         bias = bias_of() if bias_of is not None else None
-        out = rt.ws.take("attn_out", (n, self.q_width), rt.act_dtype)
+        out = rt.ws.take("attn_out", (n, self.out_width), rt.act_dtype)
+        if not self.plain:
+            return self._attend_general(q, k, v, out, ctx, cache, kvctx, tables, bias)
         if (tables is not None and bias is None and ctx.max_q_len == 1 and ctx.n_tokens == ctx.n_requests
                 and rt.act_dtype is torch.bfloat16 and s.head_dim in kernels.MMA_HEAD_DIMS
                 and s.n_heads // s.n_kv_heads <= 16):
@@ -127,6 +155,32 @@ class PagedAttention:
                               cache.k if cache.write else None, cache.v if cache.write else None,
                               s.n_heads, s.n_kv_heads, s.head_dim, ctx.page_size, rotate_q=not q_in_kernel)
         self._attend(q, out, cache, ctx, kvctx, (cos, sin, ctx.positions) if q_in_kernel else (None, None, None), bias)
+        return out
+
+    def _attend_general(self, q, k, v, out, ctx, cache, kvctx, tables, bias) -> torch.Tensor:
+        """A layer with head norms, a multiplier per head or values of their own size: one kernel norms q and k and
+        writes keys and values into their pages (fused as the rotation and the write are for a plain layer), then
+        the general attention kernel, whose scores and weights are float32, reads everything through the block
+        table.  With a rotation as well, the norm comes first and the rotating kernel writes the cache."""
+        s = self.spec
+        eps = s.qk_norm.eps if s.qk_norm is not None else 0.0
+        kpool, vpool = (cache.k, cache.v) if cache.write else (None, None)
+        if tables is None:
+            self.position.rotate(q, k, ctx)
+            kernels.headnorm_kv_write(q, k, v, self.q_gain, self.k_gain, eps, kvctx.slot_mapping, kpool, vpool,
+                                      s.n_heads, s.n_kv_heads, s.head_dim, self.v_dim, ctx.page_size)
+        else:
+            if self.v_dim != s.head_dim:
+                raise NotImplementedError("a rotation with values of another head size than the keys is not built")
+            kernels.headnorm_kv_write(q, k, v, self.q_gain, self.k_gain, eps, None, None, None, s.n_heads,
+                                      s.n_kv_heads, s.head_dim, self.v_dim, ctx.page_size)
+            kernels.rope_kv_write(q, k, v, tables[0], tables[1], ctx.positions, kvctx.slot_mapping, kpool, vpool,
+                                  s.n_heads, s.n_kv_heads, s.head_dim, ctx.page_size)
+        group = s.n_heads // s.n_kv_heads
+        work_req, work_pair0, n_work = ctx.attention_work(group, 32)
+        kernels.attention_general(q, out, cache.k, cache.v, kvctx.block_table, ctx.q_start, ctx.ctx_before,
+                                  work_req, work_pair0, n_work, s.n_heads, s.n_kv_heads, s.head_dim,
+                                  ctx.page_size, s.window, self.scale, bias, self.head_scale, self.v_dim)
         return out
 
     def _portions_only_on_tcgen05(self, ctx) -> bool:

@@ -1,6 +1,7 @@
 """The pre-norm residual block: ``x += mixer(norm(x)); x += ff(norm(x))``
 (engine/llama_block.py:50-62).  The sums are folded into the norm that follows
-them: a block hands on the residual and a delta that is not added yet."""
+them: a block hands on the residual and a delta that is not added yet.  A block
+whose spec has no feed-forward is the first half alone."""
 
 from __future__ import annotations
 
@@ -23,22 +24,23 @@ class PreNormBlock:
         out = {}
         out.update(norm_class(spec.mixer_norm).expected_tensors(spec.mixer_norm))
         out.update(mixer_class(spec.mixer).expected_tensors(spec.mixer))
-        out.update(norm_class(spec.ff_norm).expected_tensors(spec.ff_norm))
-        out.update(feedforward_class(spec.feedforward).expected_tensors(spec.feedforward))
+        if spec.feedforward is not None:
+            out.update(norm_class(spec.ff_norm).expected_tensors(spec.ff_norm))
+            out.update(feedforward_class(spec.feedforward).expected_tensors(spec.feedforward))
         return out
 
     def __init__(self, spec, tensors, rt):
         self.spec = spec
         self.mixer_norm = build_norm(spec.mixer_norm, tensors, rt)
         self.mixer = build_mixer(spec.mixer, tensors, rt)
-        self.ff_norm = build_norm(spec.ff_norm, tensors, rt)
-        self.feedforward = build_feedforward(spec.feedforward, tensors, rt)
+        self.ff_norm = build_norm(spec.ff_norm, tensors, rt) if spec.feedforward is not None else None
+        self.feedforward = build_feedforward(spec.feedforward, tensors, rt) if spec.feedforward is not None else None
 
     @property
     def graph_safe(self) -> bool:
         """Whether a step through this block may be captured as a CUDA graph: every part says that it reads the
         batch's numbers on the device only and never waits for the device (a part that says nothing does not)."""
-        return all(getattr(p, "graph_safe", False) for p in (self.mixer, self.feedforward))
+        return all(getattr(p, "graph_safe", False) for p in (self.mixer, self.feedforward) if p is not None)
 
     def forward(self, residual, pending, ctx, cache):
         n = ctx.n_tokens
@@ -47,7 +49,7 @@ class PreNormBlock:
         # ctx.upcoming_norm tells a fused part which norm follows its product into the residual (it may prepare
         # that norm's input); ctx.handover is what the part before prepared, void as soon as the residual changes
         after_block = getattr(ctx, "norm_after_block", None)
-        ff_fuses = _fuses(self.feedforward, n, self.ff_norm)
+        ff_fuses = self.feedforward is not None and _fuses(self.feedforward, n, self.ff_norm)
         if _fuses(self.mixer, n, self.mixer_norm):
             if pending is not None:
                 kernels.residual_add(residual, pending)
@@ -59,6 +61,10 @@ class PreNormBlock:
             ctx.handover = None
             h = self.mixer_norm.add_norm(residual, pending)
             a = self.mixer.forward(h, ctx, cache)
+        if self.feedforward is None:
+            ctx.handover = None
+            ctx.upcoming_norm = None
+            return residual, a
         if ff_fuses:
             if a is not None:
                 kernels.residual_add(residual, a)

@@ -3,6 +3,10 @@
 Gate and up are one matrix product over the row-concatenated weights
 [2*intermediate, hidden]; the activation and the product by ``up`` are one
 kernel in float32 arithmetic.
+
+``PolyNormMLP``: ``down(act(up(x) + b_up)) + b_down`` with the PolyNorm activation,
+a polynomial of the normalised first three powers of each token's hidden vector
+(its bias add, sums and norms are one float32 kernel).
 """
 
 from __future__ import annotations
@@ -67,4 +71,38 @@ class GatedMLP:
         else:
             gu = self.gate_up(x, ws.take("ff_gate_up", (n, 2 * s.intermediate), dt))
             kernels.silu_mul(gu, h, interleaved=True)
+        return self.down(h, ws.take("ff_out", (n, s.hidden), dt))
+
+
+@register_feedforward("polynorm_mlp")
+class PolyNormMLP:
+    graph_safe = True
+
+    @staticmethod
+    def expected_tensors(spec):
+        out = {spec.up_proj: ExpectedTensor((spec.intermediate, spec.hidden))}
+        if spec.up_bias is not None:
+            out[spec.up_bias] = ExpectedTensor((spec.intermediate,))
+        out[spec.down_proj] = ExpectedTensor((spec.hidden, spec.intermediate))
+        if spec.down_bias is not None:
+            out[spec.down_bias] = ExpectedTensor((spec.hidden,))
+        out[spec.coef] = ExpectedTensor((4,), init="gain")
+        return out
+
+    def __init__(self, spec, tensors, rt):
+        self.spec = spec
+        self.rt = rt
+        self.up = Linear(tensors[spec.up_proj], rt, "up")            # its bias rides in the activation kernel
+        self.coef = tensors[spec.coef]
+        self.up_bias = tensors[spec.up_bias].to(self.coef.dtype) if spec.up_bias is not None else None
+        self.down = Linear(tensors[spec.down_proj], rt, "down",
+                           bias=tensors[spec.down_bias] if spec.down_bias is not None else None)
+        self.eps = float(spec.eps)
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        n = x.shape[0]
+        s, ws, dt = self.spec, self.rt.ws, self.rt.act_dtype
+        z = self.up(x, ws.take("ff_up", (n, s.intermediate), dt))
+        h = ws.take("ff_hidden", (n, s.intermediate), dt)
+        kernels.polynorm(z, self.up_bias, self.coef, h, self.eps)
         return self.down(h, ws.take("ff_out", (n, s.hidden), dt))

@@ -18,12 +18,16 @@ from .. import kernels
 
 
 class Linear:
-    def __init__(self, weight: torch.Tensor, rt, name: str = "linear"):
+    def __init__(self, weight: torch.Tensor, rt, name: str = "linear", bias: torch.Tensor | None = None):
+        """``bias`` ([out_features], optional) is added to the product by ``__call__`` (the fused streaming entries
+        ``stream`` and its helpers carry none)."""
         assert weight.dim() == 2 and weight.is_contiguous()
         self.weight = weight
         self.rt = rt
         self.name = name
         self.out_features, self.in_features = weight.shape
+        assert bias is None or tuple(bias.shape) == (self.out_features,)
+        self.bias = bias.contiguous() if bias is not None else None
 
     def streams(self, n_rows: int, normed: bool = False) -> bool:
         """True when the weight-streaming kernel of this package takes this product:
@@ -47,7 +51,13 @@ class Linear:
         return out
 
     def __call__(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-        """Write ``x @ W^T`` into ``out`` ([M, out_features], may be a column slice)."""
+        """Write ``x @ W^T`` (plus the bias, if there is one) into ``out`` ([M, out_features], may be a column slice)."""
+        self._product(x, out)
+        if self.bias is not None and x.shape[0]:
+            kernels.add_bias(out, self.bias)
+        return out
+
+    def _product(self, x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         w = self.weight
         assert x.shape[1] == self.in_features and out.shape == (x.shape[0], self.out_features)
         if x.shape[0] == 0:

@@ -119,3 +119,42 @@ class DecoderModel:
             return self.head.stream(residual, logits, m, "f32", gain, eps, row_index=ctx.logit_rows)
         h = self.final_norm.gather_norm(residual, pending, ctx.logit_rows, m)
         return self.head(h, logits)
+
+
+@register_model("bigram_decoder")
+class BigramDecoderModel(DecoderModel):
+    """``DecoderModel`` whose first residual is the token embedding plus a hashed bigram embedding
+    (``BigramDecoderSpec``).  The previous token of a sequence is part of its state: one int32 word in a state slot
+    of the cache manager beside the layers' caches, read and updated on the device by the embedding kernel, so a
+    portion of a prompt, a decoded token and a token whose id is still on the device take the same path."""
+
+    @staticmethod
+    def expected_tensors(spec) -> dict:
+        out = DecoderModel.expected_tensors(spec)
+        first = {spec.embedding: out.pop(spec.embedding), spec.bigram: ExpectedTensor((spec.bigram_buckets + 1, spec.hidden))}
+        first.update(out)
+        return first
+
+    def __init__(self, spec, tensors: dict, rt):
+        super().__init__(spec, tensors, rt)
+        if spec.bigram_buckets <= 0 or spec.bigram_mul_prev < 0 or spec.bigram_mul_cur < 0:
+            raise ValueError("a hashed bigram embedding needs a positive number of buckets and non-negative multipliers")
+        self.bigram = tensors[spec.bigram].to(self.embedding.dtype)
+        self._prev_token: torch.Tensor | None = None
+
+    def cache_requirements(self) -> list[CacheRequirement]:
+        """The layers' requirements and, after them, the model's own: the last token of every request."""
+        return super().cache_requirements() + [CacheRequirement(kind="state", state_shape=(1,), state_dtype=torch.int32)]
+
+    def bind_cache(self, manager: CacheManager) -> None:
+        super().bind_cache(manager)
+        b = manager.bindings[len(self.spec.schedule)]
+        self._prev_token = manager.state_groups[b.group].data[b.row].view(-1)     # [max_requests]
+
+    def embed(self, ctx) -> torch.Tensor:
+        s = self.spec
+        residual = self.rt.ws.take("residual", (ctx.n_tokens, s.hidden), torch.float32)
+        kernels.embed_bigram(ctx.token_ids, ctx.positions, ctx.q_start, ctx.slots, ctx.n_requests, self.embedding,
+                             self.bigram, self._prev_token, residual, s.bigram_buckets, s.bigram_mul_prev,
+                             s.bigram_mul_cur)
+        return residual

@@ -1,6 +1,8 @@
 """RMSNorm: ``x / sqrt(mean(x^2) + eps) * gain`` (engine/layers.py:11-25), with
 float32 statistics whatever the activation dtype, fused with the residual sum
-that precedes it in a pre-norm block (engine/llama_block.py:53-62)."""
+that precedes it in a pre-norm block (engine/llama_block.py:53-62).
+LayerNorm: ``(x - mean) / sqrt(variance + eps) * weight + bias`` with the variance
+the mean of the squared deviations, the same way."""
 
 from __future__ import annotations
 
@@ -37,4 +39,33 @@ class RMSNorm:
                     n_rows: int, out_name: str = "normed_rows") -> torch.Tensor:
         out = self.rt.ws.take(out_name, (n_rows, self.size), self.rt.act_dtype)
         kernels.rmsnorm(residual, delta, self.gain, out, self.eps, row_index=row_index)
+        return out
+
+
+@register_norm("layernorm")
+class LayerNorm:
+    @staticmethod
+    def expected_tensors(spec):
+        out = {spec.weight: ExpectedTensor((spec.size,), init="gain")}
+        if spec.bias is not None:
+            out[spec.bias] = ExpectedTensor((spec.size,))
+        return out
+
+    def __init__(self, spec, tensors, rt):
+        self.spec = spec
+        self.rt = rt
+        self.weight = tensors[spec.weight]
+        self.bias = tensors[spec.bias].to(self.weight.dtype) if spec.bias is not None else None
+        self.eps = float(spec.eps)
+        self.size = spec.size
+
+    def add_norm(self, residual: torch.Tensor, delta: torch.Tensor | None, out_name: str = "normed") -> torch.Tensor:
+        out = self.rt.ws.take(out_name, tuple(residual.shape), self.rt.act_dtype)
+        kernels.layernorm(residual, delta, self.weight, self.bias, out, self.eps)
+        return out
+
+    def gather_norm(self, residual: torch.Tensor, delta: torch.Tensor | None, row_index: torch.Tensor,
+                    n_rows: int, out_name: str = "normed_rows") -> torch.Tensor:
+        out = self.rt.ws.take(out_name, (n_rows, self.size), self.rt.act_dtype)
+        kernels.layernorm(residual, delta, self.weight, self.bias, out, self.eps, row_index=row_index)
         return out

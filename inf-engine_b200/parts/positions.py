@@ -15,6 +15,7 @@ import math
 
 import torch
 
+from ..weights.loader import ExpectedTensor
 from .registry import register_position
 
 
@@ -80,3 +81,45 @@ class Rotary:
 
     def rotate(self, q, k, ctx):
         return None
+
+
+def distance_bucket(n: int, n_buckets: int, max_distance: int) -> int:
+    """Row of a bucketed distance table for a key that lies ``n`` positions back.
+
+    With h = n_buckets // 2: distances below h have a row each; from there on rows are spread evenly over
+    ln(n / h) between h and ``max_distance``, and every distance from ``max_distance`` on shares the last row:
+    ``min(n_buckets - 1, h + floor(ln(n / h) / ln(max_distance / h) * (n_buckets - h)))``.
+    """
+    h = n_buckets // 2
+    if n < h:
+        return n
+    return min(n_buckets - 1, h + int(math.floor(math.log(n / h) / math.log(max_distance / h) * (n_buckets - h))))
+
+
+@register_position("bucketed_bias")
+class BucketedBias:
+    """No rotation; a learned table [n_buckets, n_heads] is added to the scores by distance (``distance_bucket``).
+    The table is unrolled once into one row per distance, [n_heads, max_distance + 1] float32, whose last column
+    stands for every larger distance: what the attention kernels take as ``score_bias``."""
+
+    @staticmethod
+    def expected_tensors(spec):
+        return {spec.table: ExpectedTensor((spec.n_buckets, spec.n_heads))}
+
+    def __init__(self, spec, tensors, rt):
+        if spec.n_buckets < 2 or spec.max_distance <= spec.n_buckets // 2:
+            raise ValueError(f"a distance table of {spec.n_buckets} rows needs max_distance above {spec.n_buckets // 2}")
+        self.spec = spec
+        rows = torch.tensor([distance_bucket(n, spec.n_buckets, spec.max_distance) for n in range(spec.max_distance + 1)],
+                            dtype=torch.long, device=rt.device)
+        assert int(rows[-1]) == spec.n_buckets - 1
+        self.bias = tensors[spec.table].float()[rows].t().contiguous()          # [n_heads, max_distance + 1]
+
+    def rotary_tables(self):
+        return None
+
+    def rotate(self, q, k, ctx):
+        return None
+
+    def score_bias(self):
+        return self.bias
