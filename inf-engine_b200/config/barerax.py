@@ -120,8 +120,8 @@ class BareraxConfig:
         buckets = _positive_int(_need(bg, "buckets", "'embedding.bigram'"), "embedding.bigram.buckets")
         mul_prev, mul_cur = _need(bg, "mul_prev", "'embedding.bigram'"), _need(bg, "mul_cur", "'embedding.bigram'")
         for name, v in (("mul_prev", mul_prev), ("mul_cur", mul_cur)):
-            if isinstance(v, bool) or not isinstance(v, int) or v < 0:
-                raise ConfigError(f"config.json: embedding.bigram.{name} must be a non-negative integer, got {v!r}")
+            if isinstance(v, bool) or not isinstance(v, int) or abs(v) >= 1 << 31:
+                raise ConfigError(f"config.json: embedding.bigram.{name} must be an integer below 2^31, got {v!r}")
         raw = _need(d, "layers", "the top level")
         if not isinstance(raw, list) or not raw:
             raise ConfigError("config.json: 'layers' must be a non-empty list")

@@ -103,7 +103,9 @@ __global__ void embed_bigram_kernel(const int* __restrict__ ids, const int* __re
     if (positions[n] > 0) {
       int prev = n > first ? ids[n - 1] : (slot >= 0 ? prev_state[slot] : 0);
       if (prev < 0 || prev >= vocab) prev = 0;
-      row = (int)(((long long)prev * mul_prev + (long long)id * mul_cur) % (long long)buckets);
+      long long hsh = ((long long)prev * mul_prev + (long long)id * mul_cur) % (long long)buckets;
+      if (hsh < 0) hsh += buckets;          // the mathematical remainder, also for a negative multiplier
+      row = (int)hsh;
     }
     if (n == first && slot >= 0) prev_state[slot] = ids[q_start[r + 1] - 1];
     s_row = row;
@@ -121,7 +123,7 @@ extern "C" int ie_embed_bigram(const int* ids, const int* positions, const int* 
                                int* prev_state, float* residual, int n_tokens, int d, int vocab, int buckets,
                                long long mul_prev, long long mul_cur, cudaStream_t stream) {
   if (n_tokens <= 0) return IE_OK;
-  if (buckets <= 0 || n_requests <= 0 || mul_prev < 0 || mul_cur < 0) return IE_BAD_SIZE;
+  if (buckets <= 0 || n_requests <= 0) return IE_BAD_SIZE;
   const int threads = d >= 1024 ? 256 : 128;
   if (table_dtype == IE_F32)
     return launch_k(embed_bigram_kernel<float>, n_tokens, threads, 0, stream, ids, positions, q_start, slots,

@@ -137,8 +137,8 @@ class BigramDecoderModel(DecoderModel):
 
     def __init__(self, spec, tensors: dict, rt):
         super().__init__(spec, tensors, rt)
-        if spec.bigram_buckets <= 0 or spec.bigram_mul_prev < 0 or spec.bigram_mul_cur < 0:
-            raise ValueError("a hashed bigram embedding needs a positive number of buckets and non-negative multipliers")
+        if spec.bigram_buckets <= 0:
+            raise ValueError("a hashed bigram embedding needs a positive number of buckets")
         self.bigram = tensors[spec.bigram].to(self.embedding.dtype)
         self._prev_token: torch.Tensor | None = None
 

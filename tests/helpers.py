@@ -177,6 +177,7 @@ class TraceBuilder:
         self.rows: dict[int, list[tuple[str, int]]] = {}
         self.held: dict[str, int] = {}
         self.max_tokens = 0
+        self.max_live = 0
 
     def step(self, entries: list[tuple[str, list[int], int]], end: list[str] = ()):
         """entries: (request id, tokens, position of the first of them); every position is wanted."""
@@ -189,6 +190,7 @@ class TraceBuilder:
             rows += [(rid, start + i) for i in range(len(toks))]
             self.held[rid] = start + len(toks)
         self.max_tokens = max(self.max_tokens, sum(round64(v) for v in self.held.values()))
+        self.max_live = max(self.max_live, len(self.held))
         for rid in end:
             self.held.pop(rid)
         self.steps.append(rec)
@@ -208,7 +210,8 @@ def run_trace(model_dir, dtype: str, trace: TraceBuilder, out_dir, vocab: int, p
     text = "".join(_json.dumps(s) + "\n" for s in trace.steps)
     proc = subprocess.run(
         [sys.executable, str(root / "bin" / "trace_run"), "--model", str(model_dir), "--dtype", dtype, "--out",
-         str(out_dir), "--max-tokens", str(trace.max_tokens), "--page-size", str(page_size), "--poison-free-pages"],
+         str(out_dir), "--max-tokens", str(trace.max_tokens), "--page-size", str(page_size), "--poison-free-pages",
+         "--max-requests", str(max(1, trace.max_live))],
         input=text, capture_output=True, text=True, timeout=600, env=dict(os.environ))
     assert proc.returncode == 0, f"trace_run failed:\n{proc.stderr[-3000:]}"
     done = [l for l in proc.stdout.splitlines() if l.startswith("done ")]

@@ -115,9 +115,10 @@ def feed_forward(x: torch.Tensor, w: dict, p: str, eps: float) -> torch.Tensor:
     return polynorm(z, w[p + "act"], eps) @ w[p + "down"].T + w[p + "down.b"]
 
 
-def forward_logits(weights: dict, cfg: dict, tokens: list[int], residuals: list | None = None) -> torch.Tensor:
-    """Logits [T, vocab] (float32) of a whole sequence; ``residuals`` collects the stream after every layer."""
-    w = {n: (t.to(F) if t.is_floating_point() else t) for n, t in weights.items()}
+def forward_logits(weights: dict, cfg: dict, tokens: list[int], residuals: list | None = None, dtype=F) -> torch.Tensor:
+    """Logits [T, vocab] (float32) of a whole sequence; ``residuals`` collects the stream after every layer.
+    ``dtype``: the arithmetic (float64; float32 shows how much of a difference is the conditioning of the input)."""
+    w = {n: (t.to(dtype) if t.is_floating_point() else t) for n, t in weights.items()}
     eps = cfg["norm"]["eps"]
     x = embed(tokens, w, cfg)
     for i, layer in enumerate(cfg["layers"]):
