@@ -367,6 +367,280 @@ def run_workload(args):
     return 0
 
 
+# ---------------------------------------------------------------- another family beside the Llama decoder
+# ``--family barerax``: prefill and decode of a Barerax model (three delta-rule layers to one attention layer, LayerNorm,
+# PolyNorm feed-forward, hashed bigram embedding) at sizes that resemble a real model's layers, beside a Llama model of
+# equal width, depth, head geometry and parameter count, and every kernel of the new family beside the like kernel
+# of the Llama path, each against its roofline.  The default workload and its JSON line are not touched by this.
+FAMILY_SIZES = {"w1024": dict(width=1024, heads=16, kv=4, inter=4096), "w2048": dict(width=2048, heads=32, kv=8, inter=8192)}
+FAMILY_LAYERS, FAMILY_VOCAB, FAMILY_HD = 4, 32768, 64
+
+
+def _family_configs(size):
+    from inf_engine_b200.config import parse_config_dict
+    z = FAMILY_SIZES[size]
+    w, H, G, inter = z["width"], z["heads"], z["kv"], z["inter"]
+    ff = inter * 3 // 2                                   # two matrices of ff against three of inter: equal parameters
+    mlp = {"kind": "dense", "ff": ff}
+    delta = {"type": "general_delta", "mixer": {"heads": H, "dim": FAMILY_HD, "decay_rank": 64}, "mlp": mlp}
+    att = {"type": "attention", "mixer": {"heads": H, "kv_heads": G, "dim": FAMILY_HD, "vdim": FAMILY_HD, "scale": FAMILY_HD ** -0.5,
+                                          "bias_max": 1024, "rel_buckets": 32}, "mlp": mlp}
+    layers = [att if i % 4 == 3 else delta for i in range(FAMILY_LAYERS)]
+    brx = parse_config_dict({"architecture": "Barerax", "vocab": FAMILY_VOCAB, "width": w, "norm": {"eps": 1e-5},
+                             "embedding": {"bigram": {"buckets": 65521, "mul_prev": 1000003, "mul_cur": 31}}, "layers": layers})
+    llama = parse_config_dict(dict(architectures=["LlamaForCausalLM"], num_hidden_layers=FAMILY_LAYERS, hidden_size=w,
+                                   num_attention_heads=H, num_key_value_heads=G, head_dim=FAMILY_HD, intermediate_size=inter,
+                                   vocab_size=FAMILY_VOCAB, rope_theta=500000.0, rms_norm_eps=1e-5, tie_word_embeddings=True,
+                                   max_position_embeddings=8192, hidden_act="silu"))
+    return brx, llama
+
+
+def _weight_bytes(runner):
+    seen, n = set(), 0
+    import torch
+    stack = [runner.model]
+    while stack:
+        o = stack.pop()
+        if id(o) in seen:
+            continue
+        seen.add(id(o))
+        if isinstance(o, torch.Tensor):
+            n += o.numel() * o.element_size()
+        elif isinstance(o, (list, tuple)):
+            stack.extend(o)
+        elif hasattr(o, "__dict__") and type(o).__module__.startswith("inf_engine_b200.parts"):
+            stack.extend(v for k, v in vars(o).items() if k not in ("rt", "spec", "_views", "_prev_token"))
+    return n
+
+
+def run_family(args):
+    import numpy as np
+    import torch
+
+    from inf_engine_b200 import Engine, StepEntry, SamplingConfig, kernels
+    from inf_engine_b200.sampling import pack_rows, request_key
+
+    if args.family != "barerax":
+        print(f"--family {args.family}: unknown (known: barerax)")
+        return 2
+    pk = peaks()
+    torch.cuda.set_device(0)
+    rng = np.random.default_rng(args.seed)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")        # larger than L2; written between timed launches
+    clocks = ClockSampler()
+    clocks.start()
+    t_all0 = time.perf_counter()
+
+    def timed(fn, reps=9, warm=3):
+        """Median device time (ms) of ``fn`` alone, L2 flushed before every timed launch."""
+        for _ in range(warm):
+            fn()
+        out = []
+        for _ in range(reps):
+            flush.fill_(1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            out.append(e0.elapsed_time(e1))
+        return sorted(out)[len(out) // 2]
+
+    def model_numbers_of(cfg, batch):
+        engine = Engine.from_random(cfg, seed=args.seed, dtype="bfloat16", n_total_blocks=(batch + 1) * POOL_CONTEXT // PAGE,
+                                    block_size=PAGE, max_requests=max(16, batch), max_tokens_per_step=8192, chunk=2048)
+        runner = engine.runner
+        V = runner.spec.vocab_size
+
+        def prefill_once():
+            runner.open("p")
+            toks = rng.integers(0, V, PROMPT_LEN).tolist()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            n0 = kernels.LAUNCHES
+            e0.record()
+            runner.step([StepEntry("p", toks, [PROMPT_LEN - 1])])
+            e1.record()
+            torch.cuda.synchronize()
+            runner.close("p")
+            return e0.elapsed_time(e1), kernels.LAUNCHES - n0
+        for _ in range(3):
+            prefill_once()
+        runs = sorted(prefill_once() for _ in range(5))
+        pre_ms, pre_launches = runs[len(runs) // 2]
+        rids = [f"d{i}" for i in range(batch)]
+        for rid in rids:
+            runner.open(rid)
+        for i in range(0, batch, 4):
+            runner.step([StepEntry(r, rng.integers(0, V, PROMPT_LEN).tolist(), []) for r in rids[i:i + 4]])
+        rows = pack_rows([SamplingConfig()] * batch, [request_key(i, 0) for i in range(batch)], V)
+        ids = torch.as_tensor(rng.integers(0, V, batch), dtype=torch.int32).cuda()
+        entries = [StepEntry(r, [0], [0]) for r in rids]
+        for _ in range(max(args.warmup, 3)):
+            _, ids = runner.step_and_sample(entries, rows, device_tokens=ids)
+        torch.cuda.synchronize()
+        n0 = kernels.LAUNCHES
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            _, ids = runner.step_and_sample(entries, rows, device_tokens=ids)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+        launches = (kernels.LAUNCHES - n0) // args.steps
+        wb = _weight_bytes(runner)
+        cache_b = runner.cache.storage_bytes()
+        for rid in rids:
+            runner.close(rid)
+        out = {"prefill_tok_s": PROMPT_LEN / pre_ms * 1e3, "prefill_ms": pre_ms, "prefill_launches": pre_launches,
+               "decode_tok_s": batch / ms * 1e3, "decode_ms_per_step": ms, "decode_launches_per_step": launches,
+               "weight_bytes": wb, "decode_weight_stream_frac": wb / (ms * 1e-3) / 1e9 / pk["hbm_gbs"]}
+        del engine, runner
+        gc.collect()
+        torch.cuda.empty_cache()
+        return out
+
+    def kernel_table(size):
+        """Every kernel of the family alone, beside the like kernel of the Llama path, at 2,048 tokens of one request
+        (prefill) and at 8 requests of one token over 2,048 keys (decode).  frac: of the HBM peak for what only moves
+        bytes, of the bf16 tensor peak for attention over a prompt."""
+        z = FAMILY_SIZES[size]
+        W, H, G, hd, inter = z["width"], z["heads"], z["kv"], FAMILY_HD, z["inter"]
+        ff = inter * 3 // 2
+        N, dev, bf = PROMPT_LEN, "cuda", torch.bfloat16
+        g = torch.Generator(device=dev).manual_seed(1)
+        rnd = lambda *shape: (torch.randn(*shape, device=dev, generator=g) * 0.5)
+        i32 = lambda v: torch.as_tensor(v, dtype=torch.int32, device=dev)
+        rows = []
+
+        def add(name, like, nbytes, ms, ms_like, nbytes_like=None, flops=None):
+            rec = {"kernel": name, "like": like, "ms": ms, "like_ms": ms_like}
+            if flops is None:
+                rec["frac_of_hbm"] = nbytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"]
+                rec["like_frac_of_hbm"] = (nbytes_like or nbytes) / (ms_like * 1e-3) / 1e9 / pk["hbm_gbs"] if ms_like else None
+            else:
+                rec["frac_of_bf16"] = flops / (ms * 1e-3) / 1e12 / pk["bf16_tflops"]
+                rec["like_frac_of_bf16"] = flops / (ms_like * 1e-3) / 1e12 / pk["bf16_tflops"] if ms_like else None
+            rows.append(rec)
+
+        # norms: residual in and out (float32) + delta in + normed out (bfloat16)
+        res, delta, out = rnd(N, W), rnd(N, W).to(bf), torch.empty(N, W, device=dev, dtype=bf)
+        gain, bias = rnd(W).to(bf), rnd(W).to(bf)
+        add("layernorm(+residual sum)", "rmsnorm(+residual sum)", N * W * (4 + 4 + 2 + 2),
+            timed(lambda: kernels.layernorm(res, delta, gain, bias, out, 1e-5)),
+            timed(lambda: kernels.rmsnorm(res, delta, gain, out, 1e-5)))
+        # activation of the feed-forward
+        z_up, h = rnd(N, ff).to(bf), torch.empty(N, ff, device=dev, dtype=bf)
+        gu, h2 = rnd(N, 2 * inter).to(bf), torch.empty(N, inter, device=dev, dtype=bf)
+        add("polynorm(+up bias)", "silu_mul", N * ff * 4, timed(lambda: kernels.polynorm(z_up, rnd(ff).to(bf), rnd(4).to(bf), h, 1e-5)),
+            timed(lambda: kernels.silu_mul(gu, h2, interleaved=True)), N * inter * 6)
+        # embedding
+        table, bigram = rnd(FAMILY_VOCAB, W).to(bf), rnd(65522, W).to(bf)
+        ids, pos = i32(rng.integers(0, FAMILY_VOCAB, N)), torch.arange(N, dtype=torch.int32, device=dev)
+        state = torch.zeros(4, dtype=torch.int32, device=dev)
+        add("embed + hashed bigram", "embed_gather", N * W * (2 + 2 + 4),
+            timed(lambda: kernels.embed_bigram(ids, pos, i32([0, N]), i32([0]), 1, table, bigram, state, res, 65521, 1000003, 31)),
+            timed(lambda: kernels.embed_gather(ids, table, res)), N * W * (2 + 4))
+        # q/k head norm + cache write against rotation + cache write
+        B = 8
+        n_pages = B * N // PAGE                              # room for 8 requests of 2,048 keys
+        qkv = rnd(N, (H + 2 * G) * hd).to(bf)
+        q, kx, v = qkv[:, :H * hd], qkv[:, H * hd:(H + G) * hd], qkv[:, (H + G) * hd:]
+        kpool = torch.zeros(n_pages, G, PAGE, hd, device=dev, dtype=bf)
+        vpool = torch.zeros_like(kpool)
+        slot_map = torch.arange(N, dtype=torch.int32, device=dev)
+        cos, sin = torch.ones(N, hd // 2, device=dev), torch.zeros(N, hd // 2, device=dev)
+        qg = (1 + 0.1 * rnd(hd)).to(bf)
+        nb = N * (H + 2 * G) * hd * 2 * 2
+        add("q/k head norm + cache write", "rotation + cache write", nb,
+            timed(lambda: kernels.headnorm_kv_write(q, kx, v, qg, qg, 1e-5, slot_map, kpool, vpool, H, G, hd, hd, PAGE)),
+            timed(lambda: kernels.rope_kv_write(q, kx, v, cos, sin, pos, slot_map, kpool, vpool, H, G, hd, PAGE)))
+        # attention over a prompt of 2,048 tokens
+        from inf_engine_b200.parts.attention import PagedAttention
+        from inf_engine_b200.parts import Runtime
+        from inf_engine_b200.engine.batch import KVGroupContext, StepContext
+        brx, llama = _family_configs(size)
+        rt = Runtime(dev, bf)
+
+        def attention_part(spec_layer, names):
+            spec = spec_layer.mixer
+            tensors = {n: (rnd(*e.shape) * 0.1).to(bf) for n, e in PagedAttention.expected_tensors(spec).items()}
+            return PagedAttention(spec, tensors, rt)
+
+        def context(q_lens, before):
+            ctx = StepContext(rt, PAGE)
+            R, n = len(q_lens), sum(q_lens)
+            ctx.n_tokens, ctx.n_requests, ctx.n_logits = n, R, 0
+            starts = [0]
+            for ql in q_lens:
+                starts.append(starts[-1] + ql)
+            per = n_pages // R
+            ctx.q_start, ctx.ctx_before = i32(starts), i32(before)
+            ctx.positions = i32([b + t for ql, b in zip(q_lens, before) for t in range(ql)])
+            ctx.slots = i32(list(range(R)))
+            table_ = torch.arange(per * R, dtype=torch.int32, device=dev).view(R, per)
+            sm = i32([(r * per + (b + t) // PAGE) * PAGE + (b + t) % PAGE for r, (ql, b) in enumerate(zip(q_lens, before)) for t in range(ql)])
+            ctx.kv = [KVGroupContext(sm, table_)]
+            ctx.host = {"q_lens": list(q_lens), "ctx_before": list(before), "q_start": starts}
+            ctx.max_q_len, ctx.max_seq_len = max(q_lens), max(b + ql for ql, b in zip(q_lens, before))
+            ctx.keys_cap = ctx.max_seq_len
+            return ctx
+
+        from inf_engine_b200.parts import CacheView
+        att_b = attention_part(brx.model_spec().layers[3], None)
+        att_l = attention_part(llama.model_spec().layers[0], None)
+        view = CacheView("kv", 0, kpool, vpool, None, True)
+        flops = 4 * H * hd * (N * (N + 1) // 2)
+        ctx_p = context([N], [0])
+        qkv_p = rnd(N, (H + 2 * G) * hd).to(bf)
+        add("attention, prompt (head norms, temperature, distance bias)", "attention, prompt (rotation)", 0,
+            timed(lambda: att_b._rotate_write_attend(qkv_p.clone(), ctx_p, view), reps=5),
+            timed(lambda: att_l._rotate_write_attend(qkv_p.clone(), ctx_p, view), reps=5), flops=flops)
+        ctx_d = context([1] * B, [N - 1] * B)                # 8 requests of 2,048 keys, one new token each
+        qkv_d = rnd(B, (H + 2 * G) * hd).to(bf)
+        kv_bytes = B * N * G * hd * 2 * 2
+        add("attention, decode b8 x 2,048 keys", "attention, decode (fused rotation)", kv_bytes,
+            timed(lambda: att_b._rotate_write_attend(qkv_d.clone(), ctx_d, view)),
+            timed(lambda: att_l._rotate_write_attend(qkv_d.clone(), ctx_d, view)))
+        # the delta rule: five projections in (bfloat16), w_pre (float32), output (bfloat16); state in and out
+        Wd = H * hd
+        proj, w_pre = rnd(N, 5 * Wd + 64).to(bf), rnd(N, Wd)
+        vec = rnd(Wd).to(bf)
+        st = torch.zeros(16, H, hd, hd, device=dev)
+        mixed = torch.empty(N, Wd, device=dev, dtype=bf)
+        views = [proj[:, i * Wd:(i + 1) * Wd] for i in range(5)]
+        run_delta = lambda n, qs, sl, R: kernels.delta_rule(views[0][:n], views[1][:n], views[2][:n], views[4][:n], views[3][:n], w_pre[:n],
+                                                             vec, vec, vec, st, mixed[:n], qs, sl, R, H, hd, 0.6, 1e-6, 1e-5)
+        qs1, sl1 = i32([0, N]), i32([0])
+        qs8, sl8 = torch.arange(B + 1, dtype=torch.int32, device=dev), torch.arange(B, dtype=torch.int32, device=dev)
+        ms_p = timed(lambda: run_delta(N, qs1, sl1, 1), reps=5)
+        ms_d = timed(lambda: run_delta(B, qs8, sl8, B))
+        rows.append({"kernel": "delta rule, prompt of 2,048 tokens (one request)", "like": None, "ms": ms_p,
+                     "frac_of_hbm": (N * Wd * (5 * 2 + 4 + 2) + 2 * H * hd * hd * 4) / (ms_p * 1e-3) / 1e9 / pk["hbm_gbs"],
+                     "note": "a token-by-token scan: latency of %d dependent steps, not bytes, bounds it" % N})
+        rows.append({"kernel": "delta rule, decode b8", "like": "attention, decode (fused rotation)", "ms": ms_d,
+                     "frac_of_hbm": (B * 2 * H * hd * hd * 4) / (ms_d * 1e-3) / 1e9 / pk["hbm_gbs"],
+                     "like_ms": rows[-2]["like_ms"], "like_frac_of_hbm": rows[-2]["like_frac_of_hbm"]})
+        return rows
+
+    sizes = {}
+    for size in (args.family_sizes.split(",") if args.family_sizes else list(FAMILY_SIZES)):
+        brx, llama = _family_configs(size)
+        rec = {"barerax": model_numbers_of(brx, args.batch), "llama": model_numbers_of(llama, args.batch)}
+        rec["kernels"] = kernel_table(size)
+        sizes[size] = rec
+    clocks.stop()
+    print(json.dumps({"impl": "ours", "family": "barerax", "dtype": "bf16", "n_gpus": 1, "steps": args.steps,
+                      "warmup": max(args.warmup, 3),
+                      "data": "synthetic: seeded random weights, uniform random prompt ids",
+                      "config": {"layers": FAMILY_LAYERS, "pattern": "delta, delta, delta, attention", "vocab": FAMILY_VOCAB,
+                                 "head_dim": FAMILY_HD, "prompt": PROMPT_LEN, "decode_batch": args.batch, "page_size": PAGE,
+                                 "l2": "a 256 MB buffer is written before every timed kernel; model steps stream their weights",
+                                 "sizes": FAMILY_SIZES},
+                      "peaks": pk, "sizes": sizes, "clocks": clocks.summary(t_all0, time.perf_counter())}))
+    return 0
+
+
 REF_DIR = os.path.join(ROOT, "baseline", "_ref")
 
 
@@ -550,6 +824,10 @@ def main():
     ap.add_argument("--no-points", action="store_true", help="leave out the batch-1 and batch-64 points")
     ap.add_argument("--no-workloads", action="store_true",
                     help="leave out the two continuous-batching workloads at the other models' sizes")
+    ap.add_argument("--family", default=None, metavar="NAME",
+                    help="instead of the default workload: prefill and decode of another model family (barerax) at sizes like "
+                         "a real model's layers, beside a Llama model of equal size, and its kernels beside the like ones")
+    ap.add_argument("--family-sizes", default=None, help="comma-separated subset of the family's sizes (w1024,w2048)")
     ap.add_argument("--workload", default=None, metavar="N:MIN:MAX:NEW[:TEMP]",
                     help="instead of the step measurements: N requests through Engine.run_offline (continuous batching)")
     args = ap.parse_args()
@@ -558,6 +836,9 @@ def main():
         return 2
     if args.impl == "reference":
         return run_reference(args)
+    if args.family:
+        args.steps = min(args.steps, 64)
+        return run_family(args)
     if args.workload:
         return run_workload(args)
     args.warmup = max(args.warmup, 3)

@@ -13,7 +13,18 @@
 // Rows of a tile are (token, head-in-group) pairs p = token*group + j of one
 // (request, kv head); a row sees keys first(p) <= key <= ctx_before + token,
 // with first = limit - window + 1 when a window is set.
+//
+// A build with -DIE_ATTN_BIAS=1 serves layers whose scores are more than scale * q.k: a float32 multiplier per
+// query head beside the scale (a learned temperature) and a float32 table of biases by distance,
+// bias[head][min(distance, last)], both applied to the float32 score before the maximum and the exponential.
+// In that build the weights also stay beyond bfloat16 where they meet the values: each is cut into a bfloat16
+// and the bfloat16 of what that left out, and both parts go through the tensor cores (a weight then carries 16
+// bits of mantissa into a float32 sum), for layers whose weights are to be as exact as their scores.
 #include "common.cuh"
+
+#ifndef IE_ATTN_BIAS
+#define IE_ATTN_BIAS 0
+#endif
 
 #ifndef IE_HD
 #define IE_HD 64
@@ -25,6 +36,16 @@ constexpr int HD = IE_HD;
 constexpr int CHUNKS = HD / 8;   // 16-byte chunks in a row of HD bfloat16
 constexpr int KSTEPS = HD / 16;  // k-steps of q k^T
 constexpr int NT_O = HD / 8;     // 8-wide output tiles
+constexpr bool BIASED = IE_ATTN_BIAS != 0;
+
+// What a bias build knows about the lane's two rows: the score's multiplier (scale * the head's own * log2 e), the
+// head's row of the bias table (times log2 e; null: none) and the table's last column.
+struct RowScore {
+  const float* b0;
+  const float* b1;
+  float sc0, sc1;
+  int last;
+};
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct MmaAttnParams {
@@ -60,7 +81,22 @@ struct MmaAttnParams {
   const float* sin_t;
   const int* positions;
   const int* slot_mapping;
+  // bias builds: bias by distance [n_heads][bias_dists] float32, already times log2(e) (null: none), and a
+  // multiplier per head [n_heads] (null: none)
+  const float* score_bias;
+  int bias_dists;
+  const float* head_scale;
 };
+
+__device__ __forceinline__ RowScore row_score(const MmaAttnParams& p, int head0, int head1) {
+  RowScore rs;
+  rs.sc0 = p.scale_log2 * (p.head_scale ? p.head_scale[head0] : 1.f);
+  rs.sc1 = p.scale_log2 * (p.head_scale ? p.head_scale[head1] : 1.f);
+  rs.b0 = p.score_bias ? p.score_bias + (size_t)head0 * p.bias_dists : nullptr;
+  rs.b1 = p.score_bias ? p.score_bias + (size_t)head1 * p.bias_dists : nullptr;
+  rs.last = p.bias_dists - 1;
+  return rs;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -108,6 +144,9 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
+// the two bfloat16 of a packed pair as float32
+__device__ __forceinline__ float bf16_lo(uint32_t x) { return __uint_as_float(x << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t x) { return __uint_as_float(x & 0xffff0000u); }
 // byte offset of 16-byte chunk `chunk` of row `row` in a tile of rows of HD bfloat16;
 // the XOR keeps the eight rows that one ldmatrix touches on different banks
 __device__ __forceinline__ uint32_t swz(int row, int chunk) {
@@ -179,7 +218,7 @@ template <int KT, bool HALF = false>
 __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[KSTEPS][4], float (&o)[NT_O][4], float (&m)[2],
                                           float (&l)[2], uint32_t ks_addr, uint32_t vs_addr, int k0, int lim0,
                                           int lim1, int first0, int first1, bool need_mask, float scale_log2,
-                                          int lane) {
+                                          int lane, const RowScore& rs) {
   constexpr int NT_S = KT / 8;
   float s[NT_S][4];
 #pragma unroll
@@ -197,6 +236,29 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[KSTEPS][4], float
     }
   }
   const int col = (lane & 3) * 2;
+  if constexpr (BIASED) {
+    // the score in the exponent's units: q.k * (scale * head's multiplier * log2 e) + bias[distance] * log2 e;
+    // a tile that lies at or beyond the table's last column for a row takes that column's value for all its keys
+    scale_log2 = 1.f;
+    const bool far0 = rs.b0 == nullptr || lim0 - (k0 + KT - 1) >= rs.last;
+    const bool far1 = rs.b1 == nullptr || lim1 - (k0 + KT - 1) >= rs.last;
+    const float c0 = rs.b0 ? __ldg(rs.b0 + rs.last) : 0.f, c1 = rs.b1 ? __ldg(rs.b1 + rs.last) : 0.f;
+#pragma unroll
+    for (int i = 0; i < NT_S; ++i) {
+      const int kp = k0 + i * 8 + col;
+      const int d0 = lim0 - kp, d1 = lim1 - kp;
+      const float b00 = far0 ? c0 : __ldg(rs.b0 + min(max(d0, 0), rs.last));
+      const float b01 = far0 ? c0 : __ldg(rs.b0 + min(max(d0 - 1, 0), rs.last));
+      s[i][0] = fmaf(s[i][0], rs.sc0, b00);
+      s[i][1] = fmaf(s[i][1], rs.sc0, b01);
+      if (!HALF) {
+        const float b10 = far1 ? c1 : __ldg(rs.b1 + min(max(d1, 0), rs.last));
+        const float b11 = far1 ? c1 : __ldg(rs.b1 + min(max(d1 - 1, 0), rs.last));
+        s[i][2] = fmaf(s[i][2], rs.sc1, b10);
+        s[i][3] = fmaf(s[i][3], rs.sc1, b11);
+      }
+    }
+  }
   float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
   for (int i = 0; i < NT_S; ++i) {
@@ -227,17 +289,21 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[KSTEPS][4], float
   m[1] = mn1;
   float sum0 = 0.f, sum1 = 0.f;
   uint32_t pf[NT_S][2];
+  uint32_t pl[BIASED ? NT_S : 1][2];     // bias builds: what the bfloat16 of a weight left out, as a bfloat16 again
 #pragma unroll
   for (int i = 0; i < NT_S; ++i) {
     const float p0 = fast_exp2(fmaf(s[i][0], scale_log2, -ms0)), p1 = fast_exp2(fmaf(s[i][1], scale_log2, -ms0));
     sum0 += p0 + p1;
     pf[i][0] = pack_bf16(p0, p1);
+    if constexpr (BIASED) pl[i][0] = pack_bf16(p0 - bf16_lo(pf[i][0]), p1 - bf16_hi(pf[i][0]));
     if (!HALF) {
       const float p2 = fast_exp2(fmaf(s[i][2], scale_log2, -ms1)), p3 = fast_exp2(fmaf(s[i][3], scale_log2, -ms1));
       sum1 += p2 + p3;
       pf[i][1] = pack_bf16(p2, p3);
+      if constexpr (BIASED) pl[i][1] = pack_bf16(p2 - bf16_lo(pf[i][1]), p3 - bf16_hi(pf[i][1]));
     } else {
       pf[i][1] = 0u;
+      if constexpr (BIASED) pl[i][1] = 0u;
     }
   }
   l[0] = l[0] * c0 + sum0;
@@ -256,6 +322,10 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[KSTEPS][4], float
 #pragma unroll
   for (int kk = 0; kk < KT / 16; ++kk) {
     const uint32_t a[4] = {pf[2 * kk][0], pf[2 * kk][1], pf[2 * kk + 1][0], pf[2 * kk + 1][1]};
+    uint32_t a_lo[4] = {0u, 0u, 0u, 0u};
+    if constexpr (BIASED) {
+      a_lo[0] = pl[2 * kk][0]; a_lo[1] = pl[2 * kk][1]; a_lo[2] = pl[2 * kk + 1][0]; a_lo[3] = pl[2 * kk + 1][1];
+    }
 #pragma unroll
     for (int d2 = 0; d2 < HD / 16; ++d2) {
       uint32_t v0, v1, v2, v3;
@@ -264,6 +334,10 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[KSTEPS][4], float
       ldmatrix_x4_trans(v0, v1, v2, v3, vs_addr + swz(key, chunk));
       mma_bf16(o[2 * d2], a, v0, v1);
       mma_bf16(o[2 * d2 + 1], a, v2, v3);
+      if constexpr (BIASED) {
+        mma_bf16(o[2 * d2], a_lo, v0, v1);
+        mma_bf16(o[2 * d2 + 1], a_lo, v2, v3);
+      }
     }
   }
 }
@@ -316,6 +390,8 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(MmaAtt
   const bf16* qr1 = v1 ? p.q + (size_t)(q0 + t1) * p.q_stride + (c * group + (pr1 - t1 * group)) * HD : nullptr;
   uint32_t qf[KSTEPS][4];
   load_q_frags(qf, qr0, qr1, lane);
+  RowScore rs = {};
+  if constexpr (BIASED) rs = row_score(p, c * group + (v0 ? pr0 - t0 * group : 0), c * group + (v1 ? pr1 - t1 * group : 0));
 
   // keys that matter to the block and to this warp
   const int last_pair = min(pair0 + PF_ROWS, n_pairs) - 1;
@@ -355,7 +431,7 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(MmaAtt
       const uint32_t sb = base + (i & 1) * PF_STAGE_BYTES;
       const bool need_mask = (k0 + PF_KT - 1 > w_min_lim) || (k0 < w_max_first);
       warp_tile<PF_KT>(qf, o, m, l, sb, sb + PF_KT * HD * 2, k0, lim0, lim1, first0, first1, need_mask,
-                       p.scale_log2, lane);
+                       p.scale_log2, lane, rs);
     }
     __syncthreads();
   }
@@ -551,7 +627,7 @@ __device__ __forceinline__ void cp_async_wait_pending(int pending) {
 
 // head size 64: at most 112 registers at 192 threads, so that the block fits beside the product kernels ahead of
 // and behind it in the stream
-__global__ void __launch_bounds__(DC_THREADS, HD <= 64 ? 3 : 2) attention_decode_kernel(MmaAttnParams p) {
+__global__ void __launch_bounds__(DC_THREADS, (HD <= 64 && !BIASED) ? 3 : 2) attention_decode_kernel(MmaAttnParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
   pdl_trigger();
   TRACE_BEGIN();
@@ -643,6 +719,8 @@ __global__ void __launch_bounds__(DC_THREADS, HD <= 64 ? 3 : 2) attention_decode
     const bf16* qr1 = v1 ? p.q + (size_t)(q0 + t1) * p.q_stride + (c * group + (pr1 - t1 * group)) * HD : nullptr;
     uint32_t qf[KSTEPS][4];
     load_q_frags(qf, qr0, qr1, lane);
+    RowScore rs = {};
+    if constexpr (BIASED) rs = row_score(p, c * group + (v0 ? pr0 - t0 * group : 0), c * group + (v1 ? pr1 - t1 * group : 0));
     if (rotate) rotate_q_frags(qf, s_cos, s_sin, lane);
     TRACE(3);                                                  // q loaded and rotated (issued)
     for (int i = 0; i < n_tiles; ++i) {
@@ -659,10 +737,10 @@ __global__ void __launch_bounds__(DC_THREADS, HD <= 64 ? 3 : 2) attention_decode
       const bool need_mask = (k0 + DC_KT - 1 > ctx) || (p.window > 0);
       if (n_pairs <= 8)
         warp_tile<DC_KT, true>(qf, o, m, l, sb, sb + DC_KT * HD * 2, k0, lim0, lim1, first0, first1, need_mask,
-                               p.scale_log2, lane);
+                               p.scale_log2, lane, rs);
       else
         warp_tile<DC_KT, false>(qf, o, m, l, sb, sb + DC_KT * HD * 2, k0, lim0, lim1, first0, first1, need_mask,
-                                p.scale_log2, lane);
+                                p.scale_log2, lane, rs);
       __syncwarp();
       if (issued < n_tiles) {
         load_kv_tile<DC_KT, 32, true>(p, table, c, k_lo + issued * DC_KT, k_hi, sb, sb + DC_KT * HD * 2, lane);
@@ -843,6 +921,7 @@ static void fill(MmaAttnParams& p, const void* q, void* out, const void* kpool, 
   p.n_splits = 0; p.split_keys = 0; p.n_blocks = 0; p.scale_log2 = scale * LOG2E;
   p.fuse = 0; p.k_new = nullptr; p.v_new = nullptr; p.kv_stride = 0; p.cos_t = nullptr; p.sin_t = nullptr;
   p.positions = nullptr; p.slot_mapping = nullptr;
+  p.score_bias = nullptr; p.bias_dists = 0; p.head_scale = nullptr;
   p.page_shift = -1;
   if ((page_size & (page_size - 1)) == 0)
     for (int b = 0; b < 31; ++b)
@@ -865,18 +944,26 @@ static int check_common(const void* q, const void* out, const void* kpool, const
 extern "C" int ie_attention_mma_head_dim() { return HD; }
 
 // rows: rows of a work item's tile, 64 or 128 (the work list must have been cut accordingly)
-extern "C" int ie_attention_prefill(const void* q, void* out, const void* kpool, const void* vpool,
+extern "C" int ie_attention_mma_biased() { return BIASED ? 1 : 0; }
+
+// score_bias (float32 [n_heads][bias_dists], times log2 e) and head_scale (float32 [n_heads]) are taken by a bias
+// build only; either may be null
+static int prefill_launch(const void* q, void* out, const void* kpool, const void* vpool,
                                     const int* block_table, const int* q_start, const int* ctx_before,
                                     const int* work_req, const int* work_pair0, int q_stride, int out_stride,
                                     int table_stride, int n_work, int n_heads, int n_kv_heads, int hd, int page_size,
-                                    int window, float scale, int rows, cudaStream_t stream) {
+                                    int window, float scale, int rows, const float* score_bias, int bias_dists,
+                                    const float* head_scale, cudaStream_t stream) {
   if (rows != 64 && rows != 128) return IE_BAD_SIZE;
   if (n_work <= 0) return IE_OK;
   int rc = check_common(q, out, kpool, vpool, q_stride, out_stride, n_heads, n_kv_heads, hd, page_size);
   if (rc) return rc;
+  if ((score_bias || head_scale) && !BIASED) return IE_BAD_SIZE;
+  if (score_bias && bias_dists <= 0) return IE_BAD_SIZE;
   MmaAttnParams p;
   fill(p, q, out, kpool, vpool, block_table, q_start, ctx_before, q_stride, out_stride, table_stride, n_heads,
        n_kv_heads, page_size, window, scale);
+  p.score_bias = score_bias; p.bias_dists = bias_dists; p.head_scale = head_scale;
   p.work_req = work_req;
   p.work_pair0 = work_pair0;
   const int smem = 2 * PF_STAGE_BYTES;
@@ -890,6 +977,27 @@ extern "C" int ie_attention_prefill(const void* q, void* out, const void* kpool,
   }
   if (rows == 128) return launch_k(attention_prefill_kernel<8>, dim3(n_work, n_kv_heads), 256, smem, stream, p);
   return launch_k(attention_prefill_kernel<4>, dim3(n_work, n_kv_heads), 128, smem, stream, p);
+}
+
+extern "C" int ie_attention_prefill(const void* q, void* out, const void* kpool, const void* vpool,
+                                    const int* block_table, const int* q_start, const int* ctx_before,
+                                    const int* work_req, const int* work_pair0, int q_stride, int out_stride,
+                                    int table_stride, int n_work, int n_heads, int n_kv_heads, int hd, int page_size,
+                                    int window, float scale, int rows, cudaStream_t stream) {
+  return prefill_launch(q, out, kpool, vpool, block_table, q_start, ctx_before, work_req, work_pair0, q_stride,
+                        out_stride, table_stride, n_work, n_heads, n_kv_heads, hd, page_size, window, scale, rows,
+                        nullptr, 0, nullptr, stream);
+}
+
+extern "C" int ie_attention_prefill_biased(const void* q, void* out, const void* kpool, const void* vpool,
+                                           const int* block_table, const int* q_start, const int* ctx_before,
+                                           const int* work_req, const int* work_pair0, int q_stride, int out_stride,
+                                           int table_stride, int n_work, int n_heads, int n_kv_heads, int hd,
+                                           int page_size, int window, float scale, int rows, const float* score_bias,
+                                           int bias_dists, const float* head_scale, cudaStream_t stream) {
+  return prefill_launch(q, out, kpool, vpool, block_table, q_start, ctx_before, work_req, work_pair0, q_stride,
+                        out_stride, table_stride, n_work, n_heads, n_kv_heads, hd, page_size, window, scale, rows,
+                        score_bias, bias_dists, head_scale, stream);
 }
 
 // Scratch needed by the decode kernel, in 4-byte words: IE_DECODE_TICKET_WORDS tickets (one per
@@ -949,6 +1057,24 @@ static int decode_launch(MmaAttnParams& p, float* scratch, int n_requests, int n
   p.cluster_merge = (!no_cluster && p.n_blocks >= 2 && p.n_blocks <= 8 && launch_blocks <= block_places) ? 1 : 0;
   dim3 grid(p.n_blocks, n_kv_heads, n_requests);
   return launch_k_cluster(attention_decode_kernel, p.cluster_merge ? p.n_blocks : 1, grid, DC_THREADS, smem, stream, p);
+}
+
+extern "C" int ie_attention_decode_biased(const void* q, void* out, const void* kpool, const void* vpool,
+                                          const int* block_table, const int* q_start, const int* ctx_before,
+                                          float* scratch, int q_stride, int out_stride, int table_stride,
+                                          int n_requests, int n_tokens, int n_heads, int n_kv_heads, int hd,
+                                          int page_size, int window, float scale, int n_splits, int split_keys,
+                                          const float* score_bias, int bias_dists, const float* head_scale,
+                                          cudaStream_t stream) {
+  if (n_requests <= 0) return IE_OK;
+  int rc = check_common(q, out, kpool, vpool, q_stride, out_stride, n_heads, n_kv_heads, hd, page_size);
+  if (rc) return rc;
+  if (!BIASED || (score_bias && bias_dists <= 0) || (n_heads / n_kv_heads) > 16) return IE_BAD_SIZE;
+  MmaAttnParams p;
+  fill(p, q, out, kpool, vpool, block_table, q_start, ctx_before, q_stride, out_stride, table_stride, n_heads,
+       n_kv_heads, page_size, window, scale);
+  p.score_bias = score_bias; p.bias_dists = bias_dists; p.head_scale = head_scale;
+  return decode_launch(p, scratch, n_requests, n_tokens, n_heads, n_kv_heads, n_splits, split_keys, stream);
 }
 
 extern "C" int ie_attention_decode(const void* q, void* out, const void* kpool, const void* vpool,

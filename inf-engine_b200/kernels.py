@@ -307,18 +307,40 @@ def sample(logits: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
 
 # ------------------------------------------------- tensor-core attention (bfloat16)
 MMA_HEAD_DIMS = (64, 128)
-_mma: dict[int, object] = {}
+_mma: dict[tuple, object] = {}
+LOG2E = 1.4426950408889634
 
 
-def attention_mma_library(head_dim: int):
-    """The tensor-core attention kernels built for one head size; compiled when first asked for."""
+def _score_extras(score_bias, head_scale, n_heads):
+    """Checks of the two optional score inputs of the bias build: ``score_bias`` float32 [n_heads, D] that already
+    carries the factor log2(e) (the kernels work in the exponent's units), ``head_scale`` float32 [n_heads]."""
+    if score_bias is not None:
+        assert score_bias.dtype is torch.float32 and score_bias.is_contiguous() and score_bias.shape[0] == n_heads
+    if head_scale is not None:
+        assert head_scale.dtype is torch.float32 and head_scale.is_contiguous() and head_scale.shape == (n_heads,)
+    return score_bias.shape[1] if score_bias is not None else 0
+
+
+def attention_mma_library(head_dim: int, biased: bool = False):
+    """The tensor-core attention kernels built for one head size; compiled when first asked for.  ``biased``: the
+    build that takes a multiplier per head and a bias by distance on the float32 scores and keeps the weights to two
+    bfloat16 terms in the product with the values."""
     if head_dim not in MMA_HEAD_DIMS:
         raise KernelError(f"tensor-core attention is built for head sizes {MMA_HEAD_DIMS}, not {head_dim}")
-    lib = _mma.get(head_dim)
+    key = (head_dim, bool(biased))
+    lib = _mma.get(key)
     if lib is None:
         defines = {"IE_HD": head_dim, **BUILD_DEFINES.get("attn_mma", {})}
-        lib = load_library(f"attn_mma_hd{head_dim}", ["attention_mma.cu"], defines, ["attention_noalloc.h"])
+        name = f"attn_mma_hd{head_dim}"
+        if biased:
+            defines["IE_ATTN_BIAS"] = 1
+            name += "_bias"
+        lib = load_library(name, ["attention_mma.cu"], defines, ["attention_noalloc.h"])
         P, I, F = c_void_p, c_int, c_float
+        lib.ie_attention_prefill_biased.argtypes = [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, I, P, P]
+        lib.ie_attention_prefill_biased.restype = c_int
+        lib.ie_attention_decode_biased.argtypes = [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, I, P, I, P, P]
+        lib.ie_attention_decode_biased.restype = c_int
         lib.ie_attention_prefill.argtypes = [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P]
         lib.ie_attention_prefill.restype = c_int
         lib.ie_attention_decode.argtypes = [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, I, P]
@@ -330,16 +352,29 @@ def attention_mma_library(head_dim: int):
         lib.ie_attention_decode_ticket_words.restype = c_longlong
         lib.ie_attention_decode_warps.restype = c_int
         lib.ie_attention_decode_max_blocks.restype = c_int
-        _mma[head_dim] = lib
+        _mma[key] = lib
         _apply_check_limits()
     return lib
 
 
 def attention_prefill_mma(q, out, kpool, vpool, block_table, q_start, ctx_before, work_req, work_pair0, n_work,
-                          n_heads, n_kv_heads, head_dim, page_size, window, scale, rows: int = 64) -> None:
+                          n_heads, n_kv_heads, head_dim, page_size, window, scale, rows: int = 64,
+                          score_bias_log2e=None, head_scale=None) -> None:
     """Causal paged attention for any mix of portions and single tokens; bfloat16; the work list cuts each
-    request's (token, head-in-group) pairs into tiles of ``rows`` (64 or 128)."""
+    request's (token, head-in-group) pairs into tiles of ``rows`` (64 or 128).  With ``score_bias_log2e`` (float32
+    [n_heads, D]: the bias by distance times log2 e, last column for every larger distance) or ``head_scale``
+    (float32 [n_heads]) the bias build of the kernel runs."""
     assert q.dtype is torch.bfloat16 and q.stride(1) == 1 and out.stride(1) == 1
+    if score_bias_log2e is not None or head_scale is not None:
+        dists = _score_extras(score_bias_log2e, head_scale, n_heads)
+        lib = attention_mma_library(head_dim, biased=True)
+        _check(lib.ie_attention_prefill_biased(_ptr(q), _ptr(out), _ptr(kpool), _ptr(vpool), _ptr(block_table),
+                                               _ptr(q_start), _ptr(ctx_before), _ptr(work_req), _ptr(work_pair0),
+                                               q.stride(0), out.stride(0), block_table.stride(0), n_work, n_heads,
+                                               n_kv_heads, head_dim, page_size, int(window or 0), float(scale), rows,
+                                               _ptr(score_bias_log2e), dists, _ptr(head_scale), _stream()),
+               "attention_prefill_mma (bias build)")
+        return
     lib = attention_mma_library(head_dim)
     _check(lib.ie_attention_prefill(_ptr(q), _ptr(out), _ptr(kpool), _ptr(vpool), _ptr(block_table), _ptr(q_start),
                                     _ptr(ctx_before), _ptr(work_req), _ptr(work_pair0), q.stride(0), out.stride(0),
@@ -348,6 +383,7 @@ def attention_prefill_mma(q, out, kpool, vpool, block_table, q_start, ctx_before
 
 
 def attention_decode_scratch_floats(n_tokens, n_heads, n_splits, head_dim) -> int:
+    # (the same in both builds of a head size)
     return int(attention_mma_library(head_dim).ie_attention_decode_scratch_floats(n_tokens, n_heads, n_splits))
 
 
@@ -364,7 +400,8 @@ def attention_decode_ticket_words(head_dim) -> int:
 
 
 def attention_decode_mma(q, out, kpool, vpool, block_table, q_start, ctx_before, scratch, n_requests, n_tokens,
-                         n_heads, n_kv_heads, head_dim, page_size, window, scale, n_splits, split_keys) -> None:
+                         n_heads, n_kv_heads, head_dim, page_size, window, scale, n_splits, split_keys,
+                         score_bias_log2e=None, head_scale=None) -> None:
     """Split-key attention for steps where every request brings at most 16 (token, head-in-group) rows.
 
     ``scratch`` is float32 device memory of ``attention_decode_scratch_floats`` elements: partial
@@ -373,6 +410,16 @@ def attention_decode_mma(q, out, kpool, vpool, block_table, q_start, ctx_before,
     every block, which are written before they are read.  At most warps x blocks of
     ``attention_decode_geometry`` splits, each a multiple of 32 keys."""
     assert q.dtype is torch.bfloat16 and scratch.dtype is torch.float32
+    if score_bias_log2e is not None or head_scale is not None:       # as for the prefill kernel: the bias build
+        dists = _score_extras(score_bias_log2e, head_scale, n_heads)
+        lib = attention_mma_library(head_dim, biased=True)
+        _check(lib.ie_attention_decode_biased(_ptr(q), _ptr(out), _ptr(kpool), _ptr(vpool), _ptr(block_table),
+                                              _ptr(q_start), _ptr(ctx_before), _ptr(scratch), q.stride(0),
+                                              out.stride(0), block_table.stride(0), n_requests, n_tokens, n_heads,
+                                              n_kv_heads, head_dim, page_size, int(window or 0), float(scale), n_splits,
+                                              split_keys, _ptr(score_bias_log2e), dists, _ptr(head_scale), _stream()),
+               "attention_decode_mma (bias build)")
+        return
     lib = attention_mma_library(head_dim)
     _check(lib.ie_attention_decode(_ptr(q), _ptr(out), _ptr(kpool), _ptr(vpool), _ptr(block_table), _ptr(q_start),
                                    _ptr(ctx_before), _ptr(scratch), q.stride(0), out.stride(0),

@@ -176,12 +176,18 @@ class PagedAttention:
                                       s.n_kv_heads, s.head_dim, self.v_dim, ctx.page_size)
             kernels.rope_kv_write(q, k, v, tables[0], tables[1], ctx.positions, kvctx.slot_mapping, kpool, vpool,
                                   s.n_heads, s.n_kv_heads, s.head_dim, ctx.page_size)
-        group = s.n_heads // s.n_kv_heads
-        work_req, work_pair0, n_work = ctx.attention_work(group, 32)
-        kernels.attention_general(q, out, cache.k, cache.v, kvctx.block_table, ctx.q_start, ctx.ctx_before,
-                                  work_req, work_pair0, n_work, s.n_heads, s.n_kv_heads, s.head_dim,
-                                  ctx.page_size, s.window, self.scale, bias, self.head_scale, self.v_dim)
+        self._attend(q, out, cache, ctx, kvctx, bias=bias, head_scale=self.head_scale)
         return out
+
+    def _bias_log2e(self, bias):
+        """The bias table in the exponent's units (times log2 e), as the tensor-core kernels' bias build takes it."""
+        if bias is None:
+            return None
+        got = getattr(self, "_bias_scaled", None)
+        if got is None or got[0] is not bias:
+            got = (bias, (bias * kernels.LOG2E).contiguous())
+            self._bias_scaled = got
+        return got[1]
 
     def _portions_only_on_tcgen05(self, ctx) -> bool:
         s = self.spec
@@ -199,10 +205,15 @@ class PagedAttention:
         n = kernels.attention_decode_scratch_floats(ctx.n_tokens, s.n_heads, n_splits, s.head_dim)
         return self.rt.ws.take("attn_scratch", (n,), torch.float32)   # zero when made; tickets stay zero
 
-    def _attend(self, q, out, cache, ctx, kvctx, rotate=(None, None, None), bias=None) -> None:
+    def _attend(self, q, out, cache, ctx, kvctx, rotate=(None, None, None), bias=None, head_scale=None) -> None:
         s = self.spec
         group = s.n_heads // s.n_kv_heads
-        if bias is None and self.rt.act_dtype is torch.bfloat16 and s.head_dim in kernels.MMA_HEAD_DIMS:
+        extras = bias is not None or head_scale is not None
+        # a bias by distance or a multiplier per head: the bias build of the mma.sync kernels (scores, maxima and
+        # sums in float32, weights to two bfloat16 terms); the tcgen05 kernel has no such input
+        if (self.rt.act_dtype is torch.bfloat16 and s.head_dim in kernels.MMA_HEAD_DIMS and self.v_dim == s.head_dim
+                and (not extras or group <= 16)):
+            extra = dict(score_bias_log2e=self._bias_log2e(bias), head_scale=head_scale) if extras else {}
             # tensor-core kernels, built for this head size when first used
             n_small, small_keys = (ctx.n_requests, ctx.keys_cap) if ctx.max_q_len * group <= 16 \
                 else ctx.keys_of_small_requests(group, 16)
@@ -218,11 +229,11 @@ class PagedAttention:
                 kernels.attention_decode_mma(q, out, cache.k, cache.v, kvctx.block_table, ctx.q_start,
                                              ctx.ctx_before, scratch, ctx.n_requests, ctx.n_tokens, s.n_heads,
                                              s.n_kv_heads, s.head_dim, ctx.page_size, s.window, self.scale,
-                                             n_splits, split_keys)
+                                             n_splits, split_keys, **extra)
             if n_small == ctx.n_requests:
                 return
             more_than = 16 if n_small else 0
-            if (ctx.max_q_len * group >= TCGEN05_MIN_ROWS
+            if (not extras and ctx.max_q_len * group >= TCGEN05_MIN_ROWS
                     and kernels.attention_tcgen05_supports(s.head_dim, ctx.page_size, s.window)):
                 # prompt portions: tcgen05 tensor cores, tiles of 128 rows by 128 keys
                 work_req, work_pair0, n_work = ctx.attention_work(group, 128, more_than)
@@ -234,12 +245,13 @@ class PagedAttention:
                 work_req, work_pair0, n_work = ctx.attention_work(group, rows, more_than)
                 kernels.attention_prefill_mma(q, out, cache.k, cache.v, kvctx.block_table, ctx.q_start,
                                               ctx.ctx_before, work_req, work_pair0, n_work, s.n_heads,
-                                              s.n_kv_heads, s.head_dim, ctx.page_size, s.window, self.scale, rows)
+                                              s.n_kv_heads, s.head_dim, ctx.page_size, s.window, self.scale, rows,
+                                              **extra)
             return
         work_req, work_pair0, n_work = ctx.attention_work(group, 32)
         kernels.attention_general(q, out, cache.k, cache.v, kvctx.block_table, ctx.q_start, ctx.ctx_before,
                                   work_req, work_pair0, n_work, s.n_heads, s.n_kv_heads, s.head_dim,
-                                  ctx.page_size, s.window, self.scale, bias)
+                                  ctx.page_size, s.window, self.scale, bias, head_scale, self.v_dim)
 
 
 # fewer (token, head-in-group) rows than this in every request: the 64-row mma.sync tiles waste less

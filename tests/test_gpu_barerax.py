@@ -160,19 +160,20 @@ def test_delta_rule_kernel(dtype, dim, heads):
     assert torch.equal(state, before)
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("dtype, tensor_cores", [("float32", False), ("bfloat16", False), ("bfloat16", True)])
 @pytest.mark.parametrize("decode", [False, True])
-def test_a_far_key_stands_out_at_every_edge_of_the_distance_table(dtype, decode):
+def test_a_far_key_stands_out_at_every_edge_of_the_distance_table(dtype, tensor_cores, decode):
     """One key carries the direction that a query asks for, scaled so that its score beats all others by far; the
     value that comes back must be that key's.  The key is placed at every distance around the edges of the table's
     rows and around its far end, on both sides of page borders, and the table holds a different large value in every
-    row for every head, so that a distance that falls into the neighbouring row moves the weights visibly."""
+    row for every head, so that a distance that falls into the neighbouring row moves the weights visibly.
+    ``tensor_cores``: the bias build of the mma.sync kernels (heads of 64) instead of the general kernel."""
     from inf_engine_b200.parts import distance_bucket
 
     torch.manual_seed(5)
     act = TORCH[dtype]
-    H, G, hd, hdv, ps, rows, far = 4, 2, 16, 24, 8, 10, 37
-    T = 90
+    H, G, hd, hdv, ps, rows, far = (4, 2, 64, 64, 16, 10, 37) if tensor_cores else (4, 2, 16, 24, 8, 10, 37)
+    T = 150 if tensor_cores else 90
     table = torch.tensor([[(-1.0) ** (r + h) * (1.0 + 0.7 * r) for h in range(H)] for r in range(rows)])
     bias = table[[distance_bucket(n, rows, far) for n in range(far + 1)]].t().contiguous()      # [H, far + 1]
     temp = torch.tensor([0.7, 1.0, 1.6, 1.2])
@@ -207,7 +208,19 @@ def test_a_far_key_stands_out_at_every_edge_of_the_distance_table(dtype, decode)
         k().headnorm_kv_write(qd, kx.to(DEV), v.to(DEV), None, None, 0.0, slot_map, kpool, vpool, H, G, hd, hdv, ps)
         out = torch.empty(T, H * hdv, device=DEV, dtype=act)
         table_dev = dev_i32([order]).view(1, n_pages)
-        if decode:      # the last token alone against the cache
+        if tensor_cores and decode:
+            from inf_engine_b200.parts.attention import decode_splits
+            n_splits, split_keys = decode_splits(T, G, *k().attention_decode_geometry(hd))
+            scratch = torch.zeros(k().attention_decode_scratch_floats(1, H, n_splits, hd), device=DEV)
+            k().attention_decode_mma(qd[T - 1:], out[T - 1:], kpool, vpool, table_dev, dev_i32([0, 1]), dev_i32([T - 1]),
+                                     scratch, 1, 1, H, G, hd, ps, None, scale, n_splits, split_keys,
+                                     score_bias_log2e=(bias * k().LOG2E).to(DEV), head_scale=temp.to(DEV))
+        elif tensor_cores:
+            n_tiles = -(-T * (H // G) // 64)
+            k().attention_prefill_mma(qd, out, kpool, vpool, table_dev, dev_i32([0, T]), dev_i32([0]), dev_i32([0] * n_tiles),
+                                      dev_i32([64 * i for i in range(n_tiles)]), n_tiles, H, G, hd, ps, None, scale, 64,
+                                      score_bias_log2e=(bias * k().LOG2E).to(DEV), head_scale=temp.to(DEV))
+        elif decode:      # the last token alone against the cache
             k().attention_general(qd[T - 1:], out[T - 1:], kpool, vpool, table_dev, dev_i32([0, 1]), dev_i32([T - 1]),
                                   dev_i32([0]), dev_i32([0]), 1, H, G, hd, ps, None, scale, bias.to(DEV), temp.to(DEV), hdv)
         else:
