@@ -10,13 +10,16 @@
 // projection.  Everything between the projections and that last store is float32.
 //
 // The head size D is a compile-time constant (-DIE_DR_DIM): a library is built per size when a model first asks.
-// A block owns one (request, head) and has one thread per value column: thread j keeps column j of S (D
-// registers).  With that layout u^T S, the update and S^T r are sums inside a thread; nothing crosses threads
-// but the two norms.  The step's tokens of the request are walked in tiles: (A) the warps prepare the tile's
-// k, r, w, a*u and u in shared memory, a warp per token; (B) every thread runs the tile's tokens in order,
-// reading those vectors as broadcasts; (C) the warps norm and gate the tile's outputs, a warp per token.
-// The order of every sum is fixed by the token and the channel alone, so a token's result does not depend on
-// how the sequence was cut into steps or on what else the step holds.  A decode step is a tile of one token.
+// A block owns one (request, head).  A column of S (one value channel) belongs to KS neighbouring threads, each
+// with D / KS of its rows in registers: u^T S, the update and S^T r are sums inside a thread and a shuffle
+// among those KS lanes; nothing else crosses threads but the two norms.  The step's tokens of the request are
+// walked in tiles of TT: the tile's six inputs are fetched into registers by all threads (one batch of
+// independent loads, issued while the tile before is being run); then (A) they go to shared memory as k, r,
+// decay, rate, gate * gain and v, and a warp per token turns k and rate into u and rate * u; (B) every thread
+// runs the tile's tokens in order, reading those vectors as broadcasts; (C) a warp per token norms and gates
+// the outputs.  The order of every sum is fixed by the token and the channel alone, so a token's result does
+// not depend on how the sequence was cut into steps or on what else the step holds.  A decode step is a tile
+// of one token.
 #include "common.cuh"
 
 #ifndef IE_DR_DIM
@@ -24,9 +27,19 @@
 #endif
 #define DR_D IE_DR_DIM
 #define DR_TT (DR_D > 64 ? 8 : 16)                 // tokens a tile
-#define DR_THREADS (((DR_D + 31) / 32) * 32)
+#define DR_KS ((DR_D % 4 == 0 && DR_D > 32) ? 4 : ((DR_D % 2 == 0 && DR_D > 16) ? 2 : 1))   // threads a column
+#define DR_DK (DR_D / DR_KS)                       // rows of a column in one thread
+#define DR_THREADS (((DR_D * DR_KS + 31) / 32) * 32)
+#define DR_PER ((DR_TT * DR_D + DR_THREADS - 1) / DR_THREADS)   // elements of a tile's input a thread fetches
+// The vectors that the KS threads of a column read by rows lie in shared memory part by part, each part DR_LD
+// floats after the one before: the four floats of padding put the parts on different banks, so that one 16-byte
+// load of a warp (KS different addresses) is served at once.
+#define DR_LD (DR_DK + (DR_KS > 1 ? 4 : 0))
+#define DR_ROW (DR_KS * DR_LD)
+#define DR_VEC (DR_DK % 4 == 0)
 
-static_assert(DR_D >= 1 && DR_D <= 128, "head sizes up to 128: a thread keeps a column of the state in registers");
+static_assert(DR_D >= 1 && DR_D <= 128, "head sizes up to 128: the threads of a column keep it in registers");
+static_assert(DR_THREADS <= 1024, "one block per head");
 
 struct DeltaRuleParams {
   const void* r;            // activation type, [N, stride]: columns of one projection buffer
@@ -52,23 +65,36 @@ struct DeltaRuleParams {
 
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + expf(-x)); }
 
+__device__ __forceinline__ int split_index(int i) { return (i / DR_DK) * DR_LD + (i % DR_DK); }   // channel -> place
+
+// sum over the KS neighbouring lanes that share a column (every lane of the warp takes part)
+__device__ __forceinline__ float column_sum(float v) {
+#pragma unroll
+  for (int o = 1; o < DR_KS; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
 template <typename TA, typename TW>
 __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(DeltaRuleParams p) {
-  __shared__ __align__(16) float sk[DR_TT][DR_D], sr[DR_TT][DR_D], sw[DR_TT][DR_D], sb[DR_TT][DR_D], su[DR_TT][DR_D],
-      so[DR_TT][DR_D];
+  __shared__ __align__(16) float sk[DR_TT][DR_ROW], sr[DR_TT][DR_ROW], sw[DR_TT][DR_ROW], sb[DR_TT][DR_ROW],
+      su[DR_TT][DR_ROW], sg[DR_TT][DR_D], sv[DR_TT][DR_D], so[DR_TT][DR_D];
   pdl_trigger();
   pdl_wait();
   const int req = blockIdx.x, h = blockIdx.y;
-  const int j = threadIdx.x;
-  const int lane = j & 31, warp = j >> 5;
+  const int tid = threadIdx.x;
+  const int lane = tid & 31, warp = tid >> 5;
   constexpr int n_warps = DR_THREADS / 32;
+  const int j = tid / DR_KS, part = tid - j * DR_KS;      // this thread's column and which rows of it
+  const bool active = j < DR_D;
+  const int row0 = part * DR_DK;       // first row of the state this thread holds
+  const int base = part * DR_LD;       // where those rows' vector elements lie in shared memory
   const int q0 = p.q_start[req], q1 = p.q_start[req + 1];
   const int slot = IE_SLOT(p.slots[req]);
   const int col0 = h * DR_D;
   TA* out = (TA*)p.out;
   if (slot < 0) {
-    for (int n = q0; n < q1; ++n)
-      if (j < DR_D) out[(size_t)n * p.out_stride + col0 + j] = from_f32<TA>(0.f);
+    for (int idx = tid; idx < (q1 - q0) * DR_D; idx += DR_THREADS)
+      out[(size_t)(q0 + idx / DR_D) * p.out_stride + col0 + idx % DR_D] = from_f32<TA>(0.f);
     return;
   }
   const TA* R = (const TA*)p.r;
@@ -80,67 +106,99 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(DeltaRuleParams 
   const TW* w_bias = (const TW*)p.w_bias;
   const TW* gain = (const TW*)p.out_gain;
 
-  float S[DR_D];
+  float S[DR_DK];
   float* st = p.state + (((size_t)slot * p.n_heads + h) * DR_D) * DR_D;
-  if (j < DR_D) {
 #pragma unroll
-    for (int i = 0; i < DR_D; ++i) S[i] = st[(size_t)i * DR_D + j];
-  }
+  for (int i = 0; i < DR_DK; ++i) S[i] = active ? st[(size_t)(row0 + i) * DR_D + j] : 0.f;
+
+  // a tile's inputs in registers: element e of the tile is (token e / D, channel e % D)
+  float fk[DR_PER], fr[DR_PER], fa[DR_PER], fw[DR_PER], fg[DR_PER], fv[DR_PER];
+  auto fetch = [&](int t0, int nt) {
+#pragma unroll
+    for (int u = 0; u < DR_PER; ++u) {
+      const int e = tid + u * DR_THREADS;
+      const int tt = e / DR_D, i = e - tt * DR_D;
+      if (tt < nt) {
+        const size_t row = (size_t)(t0 + tt) * p.stride + col0 + i;
+        fk[u] = to_f32(K[row]);
+        fr[u] = to_f32(R[row]);
+        fa[u] = to_f32(A[row]);
+        fg[u] = to_f32(G[row]);
+        fv[u] = to_f32(V[row]);
+        fw[u] = p.w_pre[(size_t)(t0 + tt) * p.w_stride + col0 + i];
+      }
+    }
+  };
+  if (q0 < q1) fetch(q0, min(DR_TT, q1 - q0));
 
   for (int t0 = q0; t0 < q1; t0 += DR_TT) {
     const int nt = min(DR_TT, q1 - t0);
-    // (A) the tile's vectors, a warp per token
+    // (A) the tile's vectors into shared memory, then the unit key of every token
+#pragma unroll
+    for (int u = 0; u < DR_PER; ++u) {
+      const int e = tid + u * DR_THREADS;
+      const int tt = e / DR_D, i = e - tt * DR_D;
+      if (tt < nt) {
+        const int si = split_index(i);
+        sk[tt][si] = fk[u];
+        sr[tt][si] = fr[u];
+        sv[tt][i] = fv[u];
+        sb[tt][si] = sigmoidf_(fa[u] + to_f32(a_bias[col0 + i]));
+        sw[tt][si] = expf(-p.decay_rate * sigmoidf_(fw[u] + to_f32(w_bias[col0 + i])));
+        sg[tt][i] = to_f32(gain[col0 + i]) * sigmoidf_(fg[u]);
+      }
+    }
+    __syncthreads();
     for (int tt = warp; tt < nt; tt += n_warps) {
-      const size_t row = (size_t)(t0 + tt) * p.stride + col0;
-      const float* wp = p.w_pre + (size_t)(t0 + tt) * p.w_stride + col0;
       float ss = 0.f;
       for (int i = lane; i < DR_D; i += 32) {
-        const float kk = to_f32(K[row + i]);
+        const float kk = sk[tt][split_index(i)];
         ss += kk * kk;
       }
       const float knorm = sqrtf(warp_sum(ss) + p.key_eps);
       for (int i = lane; i < DR_D; i += 32) {
-        const float kk = to_f32(K[row + i]);
-        const float u = kk / knorm;
-        const float a = sigmoidf_(to_f32(A[row + i]) + to_f32(a_bias[col0 + i]));
-        const float w = expf(-p.decay_rate * sigmoidf_(wp[i] + to_f32(w_bias[col0 + i])));
-        sk[tt][i] = kk;
-        sr[tt][i] = to_f32(R[row + i]);
-        sw[tt][i] = w;
-        sb[tt][i] = a * u;
-        su[tt][i] = u;
+        const int si = split_index(i);
+        const float u = sk[tt][si] / knorm;
+        su[tt][si] = u;
+        sb[tt][si] *= u;
       }
-    }
-    float vv[DR_TT];
-    if (j < DR_D) {
-#pragma unroll
-      for (int tt = 0; tt < DR_TT; ++tt) vv[tt] = tt < nt ? to_f32(V[(size_t)(t0 + tt) * p.stride + col0 + j]) : 0.f;
     }
     __syncthreads();
-    // (B) the tile's tokens in order; this thread's column of the state
-    if (j < DR_D) {
+    if (t0 + DR_TT < q1) fetch(t0 + DR_TT, min(DR_TT, q1 - t0 - DR_TT));     // lands while this tile runs
+    // (B) the tile's tokens in order; this thread's rows of its column of the state
+#pragma unroll 1
+    for (int tt = 0; tt < nt; ++tt) {
+      float uu[DR_DK], bb[DR_DK], kk[DR_DK], ww[DR_DK], rr[DR_DK];
+      if constexpr (DR_VEC) {       // 16 bytes a load: a fifth of the loads of the scalar form
 #pragma unroll
-      for (int tt = 0; tt < DR_TT; ++tt) {
-        if (tt < nt) {
-          float us0 = 0.f, us1 = 0.f, us2 = 0.f, us3 = 0.f;
+        for (int i = 0; i < DR_DK; i += 4) {
+          *reinterpret_cast<float4*>(&uu[i]) = *reinterpret_cast<const float4*>(&su[tt][base + i]);
+          *reinterpret_cast<float4*>(&bb[i]) = *reinterpret_cast<const float4*>(&sb[tt][base + i]);
+          *reinterpret_cast<float4*>(&kk[i]) = *reinterpret_cast<const float4*>(&sk[tt][base + i]);
+          *reinterpret_cast<float4*>(&ww[i]) = *reinterpret_cast<const float4*>(&sw[tt][base + i]);
+          *reinterpret_cast<float4*>(&rr[i]) = *reinterpret_cast<const float4*>(&sr[tt][base + i]);
+        }
+      } else {
 #pragma unroll
-          for (int i = 0; i < DR_D; ++i) {
-            const float t = su[tt][i] * S[i];
-            if ((i & 3) == 0) us0 += t; else if ((i & 3) == 1) us1 += t; else if ((i & 3) == 2) us2 += t; else us3 += t;
-          }
-          const float us = (us0 + us1) + (us2 + us3);
-          const float vj = vv[tt];
-          float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
-#pragma unroll
-          for (int i = 0; i < DR_D; ++i) {
-            const float add = fmaf(-sb[tt][i], us, sk[tt][i] * vj);
-            S[i] = fmaf(sw[tt][i], S[i], add);
-            const float t = S[i] * sr[tt][i];
-            if ((i & 3) == 0) o0 += t; else if ((i & 3) == 1) o1 += t; else if ((i & 3) == 2) o2 += t; else o3 += t;
-          }
-          so[tt][j] = (o0 + o1) + (o2 + o3);
+        for (int i = 0; i < DR_DK; ++i) {
+          uu[i] = su[tt][base + i]; bb[i] = sb[tt][base + i]; kk[i] = sk[tt][base + i];
+          ww[i] = sw[tt][base + i]; rr[i] = sr[tt][base + i];
         }
       }
+      const float vj = active ? sv[tt][j] : 0.f;
+      float us[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int i = 0; i < DR_DK; ++i) us[i & 3] = fmaf(uu[i], S[i], us[i & 3]);
+      const float seen = column_sum((us[0] + us[1]) + (us[2] + us[3]));
+      float oo[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int i = 0; i < DR_DK; ++i) {
+        const float add = fmaf(-bb[i], seen, kk[i] * vj);
+        S[i] = fmaf(ww[i], S[i], add);
+        oo[i & 3] = fmaf(S[i], rr[i], oo[i & 3]);
+      }
+      const float o = column_sum((oo[0] + oo[1]) + (oo[2] + oo[3]));
+      if (active && part == 0) so[tt][j] = o;
     }
     __syncthreads();
     // (C) norm over the head, gain, gate; a warp per token
@@ -148,17 +206,14 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(DeltaRuleParams 
       float ss = 0.f;
       for (int i = lane; i < DR_D; i += 32) ss += so[tt][i] * so[tt][i];
       const float rms = sqrtf(warp_sum(ss) / (float)DR_D + p.norm_eps);
-      const size_t row = (size_t)(t0 + tt) * p.stride + col0;
-      for (int i = lane; i < DR_D; i += 32) {
-        const float y = so[tt][i] / rms * to_f32(gain[col0 + i]) * sigmoidf_(to_f32(G[row + i]));
-        out[(size_t)(t0 + tt) * p.out_stride + col0 + i] = from_f32<TA>(y);
-      }
+      for (int i = lane; i < DR_D; i += 32)
+        out[(size_t)(t0 + tt) * p.out_stride + col0 + i] = from_f32<TA>(so[tt][i] / rms * sg[tt][i]);
     }
     __syncthreads();
   }
-  if (p.write_state && j < DR_D) {
+  if (p.write_state && active) {
 #pragma unroll
-    for (int i = 0; i < DR_D; ++i) st[(size_t)i * DR_D + j] = S[i];
+    for (int i = 0; i < DR_DK; ++i) st[(size_t)(row0 + i) * DR_D + j] = S[i];
   }
 }
 

@@ -157,7 +157,7 @@ static int launch_rmsnorm(float* residual, const void* delta, const void* gain, 
                     (bf16*)out, row_index, d, eps);
   const size_t smem = (size_t)d * sizeof(float);
   if (smem > 200 * 1024) return IE_BAD_SIZE;
-  if (smem > 48 * 1024) {
+  if (smem > 47 * 1024) {      // the static reduction scratch counts towards the 48 KB that need no opt-in
     cudaError_t e = cudaFuncSetAttribute(rmsnorm_kernel<TA, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }

@@ -89,10 +89,11 @@ def test_polynorm_kernel(dtype):
     assert close(out, plain.polynorm(z.double(), coef.double(), 1e-6), dtype)
 
 
-def test_bigram_embedding_kernel_keeps_the_last_token_of_every_request():
+@pytest.mark.parametrize("dtype, d", [("float32", 24), ("bfloat16", 24), ("bfloat16", 20)])
+def test_bigram_embedding_kernel_keeps_the_last_token_of_every_request(dtype, d):
     torch.manual_seed(3)
-    vocab, d, buckets, mp, mc = 50, 24, 13, 1000003, 7
-    table, bigram = torch.randn(vocab, d), torch.randn(buckets + 1, d)
+    vocab, buckets, mp, mc = 50, 13, 1000003, 7
+    table, bigram = torch.randn(vocab, d).to(TORCH[dtype]), torch.randn(buckets + 1, d).to(TORCH[dtype])
     # request 0 starts (3 tokens), request 1 goes on from position 9 after token 41 (1 token), request 2 is padding
     ids = [4, 4, 17, 30, 0]
     state = dev_i32([0, 41, 99, 0])
@@ -100,18 +101,18 @@ def test_bigram_embedding_kernel_keeps_the_last_token_of_every_request():
     k().embed_bigram(dev_i32(ids), dev_i32([0, 1, 2, 9, 0]), dev_i32([0, 3, 4, 5]), dev_i32([2, 1, -1]), 3,
                      table.to(DEV), bigram.to(DEV), state, res, buckets, mp, mc)
     rows = [buckets, (4 * mp + 4 * mc) % buckets, (4 * mp + 17 * mc) % buckets, (41 * mp + 30 * mc) % buckets, buckets]
-    want = table[ids] + bigram[rows]
+    want = table[ids].float() + bigram[rows].float()
     assert torch.equal(res.cpu(), want)
     assert state.tolist() == [0, 30, 17, 0]
     # the next step of request 0 takes its previous token from the slot
     k().embed_bigram(dev_i32([9, 2]), dev_i32([3, 4]), dev_i32([0, 2]), dev_i32([2]), 1, table.to(DEV), bigram.to(DEV),
                      state, res[:2], buckets, mp, mc)
-    assert torch.equal(res[:2].cpu(), table[[9, 2]] + bigram[[(17 * mp + 9 * mc) % buckets, (9 * mp + 2 * mc) % buckets]])
+    assert torch.equal(res[:2].cpu(), table[[9, 2]].float() + bigram[[(17 * mp + 9 * mc) % buckets, (9 * mp + 2 * mc) % buckets]].float())
     assert state.tolist() == [0, 30, 2, 0]
     # a negative multiplier: the remainder is the mathematical one, never negative
     k().embed_bigram(dev_i32([9, 2]), dev_i32([3, 4]), dev_i32([0, 2]), dev_i32([2]), 1, table.to(DEV), bigram.to(DEV),
                      state, res[:2], buckets, -5, 3)
-    assert torch.equal(res[:2].cpu(), table[[9, 2]] + bigram[[(2 * -5 + 9 * 3) % buckets, (9 * -5 + 2 * 3) % buckets]])
+    assert torch.equal(res[:2].cpu(), table[[9, 2]].float() + bigram[[(2 * -5 + 9 * 3) % buckets, (9 * -5 + 2 * 3) % buckets]].float())
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
