@@ -27,7 +27,13 @@
 #endif
 #define DR_D IE_DR_DIM
 #define DR_TT (DR_D > 64 ? 8 : 16)                 // tokens a tile
-#define DR_KS ((DR_D % 4 == 0 && DR_D > 32) ? 4 : ((DR_D % 2 == 0 && DR_D > 16) ? 2 : 1))   // threads a column
+#ifdef IE_DR_KS
+#define DR_KS IE_DR_KS                             // threads a column (a build may say; measurements)
+#else
+// threads a column; measured on a B200 over a prompt of 2,048 tokens, 1,024 channels: heads of 64: 4, 2, 1 threads
+// take 1.34, 1.45, 2.44 ms; heads of 128: 3.56, 2.50, 3.36 ms
+#define DR_KS (DR_D > 64 ? (DR_D % 2 == 0 ? 2 : 1) : ((DR_D % 4 == 0 && DR_D > 32) ? 4 : ((DR_D % 2 == 0 && DR_D > 16) ? 2 : 1)))
+#endif
 #define DR_DK (DR_D / DR_KS)                       // rows of a column in one thread
 #define DR_THREADS (((DR_D * DR_KS + 31) / 32) * 32)
 #define DR_PER ((DR_TT * DR_D + DR_THREADS - 1) / DR_THREADS)   // elements of a tile's input a thread fetches
@@ -130,6 +136,15 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(DeltaRuleParams 
     }
   };
   if (q0 < q1) fetch(q0, min(DR_TT, q1 - q0));
+  // the channel of element u of this thread is the same in every tile: its three constants are read once
+  float c_ab[DR_PER], c_wb[DR_PER], c_gn[DR_PER];
+#pragma unroll
+  for (int u = 0; u < DR_PER; ++u) {
+    const int i = (tid + u * DR_THREADS) % DR_D;
+    c_ab[u] = to_f32(a_bias[col0 + i]);
+    c_wb[u] = to_f32(w_bias[col0 + i]);
+    c_gn[u] = to_f32(gain[col0 + i]);
+  }
 
   for (int t0 = q0; t0 < q1; t0 += DR_TT) {
     const int nt = min(DR_TT, q1 - t0);
@@ -143,9 +158,9 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(DeltaRuleParams 
         sk[tt][si] = fk[u];
         sr[tt][si] = fr[u];
         sv[tt][i] = fv[u];
-        sb[tt][si] = sigmoidf_(fa[u] + to_f32(a_bias[col0 + i]));
-        sw[tt][si] = expf(-p.decay_rate * sigmoidf_(fw[u] + to_f32(w_bias[col0 + i])));
-        sg[tt][i] = to_f32(gain[col0 + i]) * sigmoidf_(fg[u]);
+        sb[tt][si] = sigmoidf_(fa[u] + c_ab[u]);
+        sw[tt][si] = expf(-p.decay_rate * sigmoidf_(fw[u] + c_wb[u]));
+        sg[tt][i] = c_gn[u] * sigmoidf_(fg[u]);
       }
     }
     __syncthreads();
@@ -166,7 +181,7 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(DeltaRuleParams 
     __syncthreads();
     if (t0 + DR_TT < q1) fetch(t0 + DR_TT, min(DR_TT, q1 - t0 - DR_TT));     // lands while this tile runs
     // (B) the tile's tokens in order; this thread's rows of its column of the state
-#pragma unroll 1
+#pragma unroll 2
     for (int tt = 0; tt < nt; ++tt) {
       float uu[DR_DK], bb[DR_DK], kk[DR_DK], ww[DR_DK], rr[DR_DK];
       if constexpr (DR_VEC) {       // 16 bytes a load: a fifth of the loads of the scalar form

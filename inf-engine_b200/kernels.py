@@ -382,21 +382,21 @@ def attention_prefill_mma(q, out, kpool, vpool, block_table, q_start, ctx_before
                                     int(window or 0), float(scale), rows, _stream()), "attention_prefill_mma")
 
 
-def attention_decode_scratch_floats(n_tokens, n_heads, n_splits, head_dim) -> int:
-    # (the same in both builds of a head size)
-    return int(attention_mma_library(head_dim).ie_attention_decode_scratch_floats(n_tokens, n_heads, n_splits))
+def attention_decode_scratch_floats(n_tokens, n_heads, n_splits, head_dim, biased: bool = False) -> int:
+    # the same in both builds of a head size; ``biased`` only says which one to ask (the one the model has loaded)
+    return int(attention_mma_library(head_dim, biased).ie_attention_decode_scratch_floats(n_tokens, n_heads, n_splits))
 
 
-def attention_decode_geometry(head_dim) -> tuple[int, int]:
+def attention_decode_geometry(head_dim, biased: bool = False) -> tuple[int, int]:
     """(warps, i.e. splits, of a decode block; the most blocks per (request, kv head) a launch takes)."""
-    lib = attention_mma_library(head_dim)
+    lib = attention_mma_library(head_dim, biased)
     return int(lib.ie_attention_decode_warps()), int(lib.ie_attention_decode_max_blocks())
 
 
-def attention_decode_ticket_words(head_dim) -> int:
+def attention_decode_ticket_words(head_dim, biased: bool = False) -> int:
     """How many words at the start of the decode scratch hold tickets; they must be zero before the
     first launch on a piece of scratch (every launch leaves them zero)."""
-    return int(attention_mma_library(head_dim).ie_attention_decode_ticket_words())
+    return int(attention_mma_library(head_dim, biased).ie_attention_decode_ticket_words())
 
 
 def attention_decode_mma(q, out, kpool, vpool, block_table, q_start, ctx_before, scratch, n_requests, n_tokens,

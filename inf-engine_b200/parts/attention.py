@@ -202,7 +202,7 @@ class PagedAttention:
 
     def _decode_scratch(self, ctx, n_splits: int) -> torch.Tensor:
         s = self.spec
-        n = kernels.attention_decode_scratch_floats(ctx.n_tokens, s.n_heads, n_splits, s.head_dim)
+        n = kernels.attention_decode_scratch_floats(ctx.n_tokens, s.n_heads, n_splits, s.head_dim, not self.plain)
         return self.rt.ws.take("attn_scratch", (n,), torch.float32)   # zero when made; tickets stay zero
 
     def _attend(self, q, out, cache, ctx, kvctx, rotate=(None, None, None), bias=None, head_scale=None) -> None:
@@ -217,13 +217,13 @@ class PagedAttention:
             # tensor-core kernels, built for this head size when first used
             n_small, small_keys = (ctx.n_requests, ctx.keys_cap) if ctx.max_q_len * group <= 16 \
                 else ctx.keys_of_small_requests(group, 16)
-            if ctx.n_requests * s.n_kv_heads > kernels.attention_decode_ticket_words(s.head_dim):
+            if ctx.n_requests * s.n_kv_heads > kernels.attention_decode_ticket_words(s.head_dim, extras):
                 n_small = 0        # more (request, kv head) pairs than the split-key kernel has tickets for
             if n_small:
                 # requests with at most 16 rows (decode tokens, as a rule): the split-key kernel; in a mixed step
                 # it leaves the others alone, and the prefill kernel below is given those only
                 n_splits, split_keys = decode_splits(small_keys, n_small * s.n_kv_heads,
-                                                      *kernels.attention_decode_geometry(s.head_dim),
+                                                      *kernels.attention_decode_geometry(s.head_dim, extras),
                                                       block_slots=2 * kernels.sm_count())
                 scratch = self._decode_scratch(ctx, n_splits)
                 kernels.attention_decode_mma(q, out, cache.k, cache.v, kvctx.block_table, ctx.q_start,
