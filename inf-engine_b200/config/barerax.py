@@ -144,7 +144,10 @@ class BareraxConfig:
                     raise ConfigError(f"config.json: {where}: {heads} heads are not a multiple of {kv} kv_heads")
                 rel = shapes.get(f"l{i}.mix.rel")
                 n_rel = int(rel[0]) if rel else int(m.get("rel_buckets", DEFAULT_REL_BUCKETS))
-                bias_max = _positive_int(_need(m, "bias_max", where + ".mixer"), where + ".mixer.bias_max")
+                bias_max = _need(m, "bias_max", where + ".mixer")
+                if isinstance(bias_max, float) and bias_max.is_integer():
+                    bias_max = int(bias_max)
+                bias_max = _positive_int(bias_max, where + ".mixer.bias_max")
                 if n_rel < 2 or bias_max <= n_rel // 2:
                     raise ConfigError(f"config.json: {where}: a distance table of {n_rel} rows needs bias_max above "
                                       f"{n_rel // 2}, got {bias_max}")

@@ -1,5 +1,5 @@
 // Paged causal attention for any mix of prompt portions and decode tokens, any
-// head size up to 256 (values: a multiple of 8), any number of heads and groups,
+// head size up to 256 (keys and values each their own), any number of heads and groups,
 // an optional window.  float32 arithmetic on CUDA cores with float32 or
 // bfloat16 storage: this is the kernel of the true 32-bit path and the fallback
 // of the bfloat16 path for sizes that the tensor-core kernels do not take.
@@ -113,7 +113,7 @@ __global__ void __launch_bounds__(AG_THREADS) attention_general_kernel(AttnGener
 #pragma unroll
   for (int i = 0; i < AG_MAX_ACC; ++i) acc[i] = 0.f;
   float m_run = -INFINITY, l_run = 0.f;
-  const int n_acc = hdv >> 3;
+  const int n_acc = (hdv + 7) >> 3;       // the last one of a value size that is no multiple of 8 is partly idle
 
   for (int kt = key_begin; kt < key_end; kt += AG_KEYS) {
     __syncthreads();  // previous tile fully consumed (and Qs staged, first time)
@@ -184,7 +184,7 @@ __global__ void __launch_bounds__(AG_THREADS) attention_general_kernel(AttnGener
     const float* pr_ = Ps + row * (AG_KEYS + 1);
 #pragma unroll
     for (int i = 0; i < AG_MAX_ACC; ++i) {
-      if (i < n_acc) {
+      if (i < n_acc && sub + 8 * i < hdv) {
         float a = acc[i] * alpha;
         const float* vcol = Vs + sub + 8 * i;
 #pragma unroll 8
@@ -200,7 +200,7 @@ __global__ void __launch_bounds__(AG_THREADS) attention_general_kernel(AttnGener
     const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
 #pragma unroll
     for (int i = 0; i < AG_MAX_ACC; ++i)
-      if (i < n_acc) o[sub + 8 * i] = from_f32<T>(acc[i] * inv);
+      if (i < n_acc && sub + 8 * i < hdv) o[sub + 8 * i] = from_f32<T>(acc[i] * inv);
   }
 }
 
@@ -212,7 +212,7 @@ extern "C" int ie_attention_general(const void* q, void* out, const void* kpool,
                                     int bias_dists, const float* head_scale, int hd_v, cudaStream_t stream) {
   if (n_work <= 0) return IE_OK;
   if (hd_v <= 0) hd_v = hd;
-  if (hd <= 0 || hd > 8 * AG_MAX_ACC || hd_v % 8 || hd_v > 8 * AG_MAX_ACC) return IE_BAD_SIZE;
+  if (hd <= 0 || hd > 8 * AG_MAX_ACC || hd_v > 8 * AG_MAX_ACC) return IE_BAD_SIZE;
   if (n_kv_heads <= 0 || n_heads % n_kv_heads) return IE_BAD_SIZE;
   if (score_bias != nullptr && bias_dists <= 0) return IE_BAD_SIZE;
   AttnGeneralParams p;

@@ -72,7 +72,8 @@ def main(argv=None) -> int:
             if not runner.is_open(rid):
                 if not runner.open(rid):
                     raise RuntimeError(f"step {step}: more than {args.max_requests} live requests")
-            entries.append(StepEntry(rid, [int(t) for t in e["tokens"]], [int(w) for w in e.get("want", [])]))
+            if e.get("tokens"):            # an entry without tokens admits its request and brings nothing to the step
+                entries.append(StepEntry(rid, [int(t) for t in e["tokens"]], [int(w) for w in e.get("want", [])]))
         logits = runner.step(entries)
         if logits is not None:
             data = logits.detach().to("cpu").contiguous().numpy().astype("<f4", copy=False)

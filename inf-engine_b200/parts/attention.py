@@ -66,9 +66,8 @@ class PagedAttention:
     def __init__(self, spec, tensors, rt):
         if spec.n_heads % spec.n_kv_heads:
             raise ValueError(f"{spec.n_heads} query heads are not a multiple of {spec.n_kv_heads} kv heads")
-        if spec.head_dim > 256 or spec.value_dim % 8 or spec.value_dim > 256:
-            raise ValueError(f"attention kernels take head sizes up to 256 (values: in steps of 8), not "
-                             f"{spec.head_dim} and {spec.value_dim}")
+        if not (0 < spec.head_dim <= 256 and 0 < spec.value_dim <= 256):
+            raise ValueError(f"attention kernels take head sizes up to 256, not {spec.head_dim} and {spec.value_dim}")
         if spec.window is not None and spec.window <= 0:
             raise ValueError("an attention window must be positive")
         self.spec = spec

@@ -53,13 +53,20 @@ BRX_C = _model(270, 128, 1e-5, 401, 1000, 3, [
     _att(1, 1, 64, 64, 0.125, 100, 20, 144),
     _delta(2, 64, 6, None),
 ])
+# sizes that are multiples of nothing: width 100, a vocabulary of 257, heads of 24 and 40 with values of 20, five heads
+# with five kv heads, a feed-forward of 100, seven table rows, one bigram bucket and a multiplier of zero
+BRX_D = _model(257, 100, 1e-5, 1, 0, 3, [
+    _att(5, 5, 40, 20, 0.15, 11, 7, 100),
+    _delta(3, 24, 3, 52),
+    _att(2, 1, 8, 4, 0.5, 50, 3, None),
+])
 # one layer each, for a mechanism alone
 BRX_ATT = _model(200, 48, 1e-5, 50, 7, 11, [_att(6, 3, 16, 8, 0.4, 24, 10, None)])
 BRX_DELTA = _model(200, 48, 1e-5, 50, 7, 11, [_delta(3, 16, 7, None)])
 BRX_FF = _model(200, 48, 1e-6, 50, 7, 11, [_delta(1, 16, 3, 104)])
 
-MODELS = {"brx_a": BRX_A, "brx_b": BRX_B, "brx_c": BRX_C, "brx_att": BRX_ATT, "brx_delta": BRX_DELTA, "brx_ff": BRX_FF}
-SEEDS = {"brx_a": 11, "brx_b": 12, "brx_c": 13, "brx_att": 14, "brx_delta": 15, "brx_ff": 16}
+MODELS = {"brx_a": BRX_A, "brx_b": BRX_B, "brx_c": BRX_C, "brx_d": BRX_D, "brx_att": BRX_ATT, "brx_delta": BRX_DELTA, "brx_ff": BRX_FF}
+SEEDS = {"brx_a": 11, "brx_b": 12, "brx_c": 13, "brx_d": 17, "brx_att": 14, "brx_delta": 15, "brx_ff": 16}
 
 
 def stated_config(d: dict) -> dict:

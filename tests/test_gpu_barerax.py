@@ -161,19 +161,19 @@ def test_delta_rule_kernel(dtype, dim, heads):
     assert torch.equal(state, before)
 
 
-@pytest.mark.parametrize("dtype, tensor_cores", [("float32", False), ("bfloat16", False), ("bfloat16", True)])
+@pytest.mark.parametrize("dtype, tensor_cores", [("float32", 0), ("bfloat16", 0), ("bfloat16", 64), ("bfloat16", 128)])
 @pytest.mark.parametrize("decode", [False, True])
 def test_a_far_key_stands_out_at_every_edge_of_the_distance_table(dtype, tensor_cores, decode):
     """One key carries the direction that a query asks for, scaled so that its score beats all others by far; the
     value that comes back must be that key's.  The key is placed at every distance around the edges of the table's
     rows and around its far end, on both sides of page borders, and the table holds a different large value in every
     row for every head, so that a distance that falls into the neighbouring row moves the weights visibly.
-    ``tensor_cores``: the bias build of the mma.sync kernels (heads of 64) instead of the general kernel."""
+    ``tensor_cores``: the bias build of the mma.sync kernels (heads of that size) instead of the general kernel."""
     from inf_engine_b200.parts import distance_bucket
 
     torch.manual_seed(5)
     act = TORCH[dtype]
-    H, G, hd, hdv, ps, rows, far = (4, 2, 64, 64, 16, 10, 37) if tensor_cores else (4, 2, 16, 24, 8, 10, 37)
+    H, G, hd, hdv, ps, rows, far = (4, 2, tensor_cores, tensor_cores, 16, 10, 37) if tensor_cores else (4, 2, 16, 24, 8, 10, 37)
     T = 150 if tensor_cores else 90
     table = torch.tensor([[(-1.0) ** (r + h) * (1.0 + 0.7 * r) for h in range(H)] for r in range(rows)])
     bias = table[[distance_bucket(n, rows, far) for n in range(far + 1)]].t().contiguous()      # [H, far + 1]
@@ -271,7 +271,7 @@ def steady_tokens(cfg, w, n: int, seed: int) -> list[int]:
     raise AssertionError("no well-conditioned first token in 50 seeds")
 
 
-LENGTH = {"brx_a": 97, "brx_b": 70, "brx_c": 131, "brx_att": 60, "brx_delta": 50, "brx_ff": 41}
+LENGTH = {"brx_a": 97, "brx_b": 70, "brx_c": 131, "brx_d": 75, "brx_att": 60, "brx_delta": 50, "brx_ff": 41}
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -292,7 +292,7 @@ def test_whole_prompt_decoding_and_portions_agree_with_the_plain_model(tmp_path,
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["brx_a", "brx_b", "brx_c"])
+@pytest.mark.parametrize("name", ["brx_a", "brx_b", "brx_c", "brx_d"])
 def test_unequal_requests_in_one_batch_with_pages_and_slots_used_again(tmp_path, name, dtype):
     """Seven requests, at most three live, portions of some beside decoded tokens of others, some left out of a step;
     the pool holds exactly what the fullest moment needs and free pages are filled with NaN."""
