@@ -71,6 +71,19 @@ struct DeltaRuleParams {
 
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + expf(-x)); }
 
+// Loads of a tile's inputs that stay where they are written (volatile): they are issued before the tile ahead is run
+// and used after it; left to itself the compiler moves them down to their use and the tile then waits for memory.
+__device__ __forceinline__ float ld_early(const float* p) {
+  float v;
+  asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ float ld_early(const bf16* p) {
+  unsigned short v;
+  asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(v) : "l"(p));
+  return __uint_as_float((unsigned)v << 16);
+}
+
 __device__ __forceinline__ int split_index(int i) { return (i / DR_DK) * DR_LD + (i % DR_DK); }   // channel -> place
 
 // sum over the KS neighbouring lanes that share a column (every lane of the warp takes part)
@@ -126,12 +139,12 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(DeltaRuleParams 
       const int tt = e / DR_D, i = e - tt * DR_D;
       if (tt < nt) {
         const size_t row = (size_t)(t0 + tt) * p.stride + col0 + i;
-        fk[u] = to_f32(K[row]);
-        fr[u] = to_f32(R[row]);
-        fa[u] = to_f32(A[row]);
-        fg[u] = to_f32(G[row]);
-        fv[u] = to_f32(V[row]);
-        fw[u] = p.w_pre[(size_t)(t0 + tt) * p.w_stride + col0 + i];
+        fk[u] = ld_early(K + row);
+        fr[u] = ld_early(R + row);
+        fa[u] = ld_early(A + row);
+        fg[u] = ld_early(G + row);
+        fv[u] = ld_early(V + row);
+        fw[u] = ld_early(p.w_pre + (size_t)(t0 + tt) * p.w_stride + col0 + i);
       }
     }
   };
@@ -205,13 +218,17 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(DeltaRuleParams 
 #pragma unroll
       for (int i = 0; i < DR_DK; ++i) us[i & 3] = fmaf(uu[i], S[i], us[i & 3]);
       const float seen = column_sum((us[0] + us[1]) + (us[2] + us[3]));
+      // one pass per operation, so that neighbouring instructions do not wait for one another
+      float add[DR_DK];
+#pragma unroll
+      for (int i = 0; i < DR_DK; ++i) add[i] = kk[i] * vj;
+#pragma unroll
+      for (int i = 0; i < DR_DK; ++i) add[i] = fmaf(-bb[i], seen, add[i]);
+#pragma unroll
+      for (int i = 0; i < DR_DK; ++i) S[i] = fmaf(ww[i], S[i], add[i]);
       float oo[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int i = 0; i < DR_DK; ++i) {
-        const float add = fmaf(-bb[i], seen, kk[i] * vj);
-        S[i] = fmaf(ww[i], S[i], add);
-        oo[i & 3] = fmaf(S[i], rr[i], oo[i & 3]);
-      }
+      for (int i = 0; i < DR_DK; ++i) oo[i & 3] = fmaf(S[i], rr[i], oo[i & 3]);
       const float o = column_sum((oo[0] + oo[1]) + (oo[2] + oo[3]));
       if (active && part == 0) so[tt][j] = o;
     }
