@@ -1,4 +1,6 @@
-"""B200-native inference engine for the dense Llama decoder (Llama 3.2, SmolLM2).
+"""B200-native inference engine for the dense Llama decoder (Llama 3.2, SmolLM2) and for the Barerax decoder
+(delta-rule layers with a state per request beside attention with a bias by distance); the architecture named in a
+model folder's ``config.json`` chooses.
 
 Public surface, in the manner of the reference's ``engine`` package
 (engine/__init__.py:39-112):
@@ -12,6 +14,7 @@ The reference's names ``LlamaPagedEngine`` and ``LlamaRequest`` are kept as alia
 
 from .cache import CacheManager, CacheRequirement, PagePool
 from .config import (
+    BareraxConfig,
     ConfigError,
     LlamaConfig,
     ModelSpec,
@@ -29,7 +32,7 @@ LlamaPagedEngine = Engine
 LlamaRequest = Request
 
 __all__ = [
-    "CacheManager", "CacheRequirement", "ConfigError", "Engine", "LlamaConfig", "LlamaPagedEngine",
+    "BareraxConfig", "CacheManager", "CacheRequirement", "ConfigError", "Engine", "LlamaConfig", "LlamaPagedEngine",
     "LlamaRequest", "ModelRunner", "ModelSpec", "OutOfPages", "PagePool", "Request", "SamplingConfig",
     "SamplingMode", "Scheduler", "StepEntry", "WeightsError", "detect_config", "get_llama_config", "get_preset",
     "load_engine", "load_weights", "parse_config_dict", "register_architecture", "write_random_model",
