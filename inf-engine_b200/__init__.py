@@ -16,6 +16,7 @@ from .cache import CacheManager, CacheRequirement, PagePool
 from .config import (
     BareraxConfig,
     ConfigError,
+    KipezenConfig,
     LlamaConfig,
     ModelSpec,
     detect_config,
@@ -32,7 +33,7 @@ LlamaPagedEngine = Engine
 LlamaRequest = Request
 
 __all__ = [
-    "BareraxConfig", "CacheManager", "CacheRequirement", "ConfigError", "Engine", "LlamaConfig", "LlamaPagedEngine",
+    "BareraxConfig", "CacheManager", "KipezenConfig", "CacheRequirement", "ConfigError", "Engine", "LlamaConfig", "LlamaPagedEngine",
     "LlamaRequest", "ModelRunner", "ModelSpec", "OutOfPages", "PagePool", "Request", "SamplingConfig",
     "SamplingMode", "Scheduler", "StepEntry", "WeightsError", "detect_config", "get_llama_config", "get_preset",
     "load_engine", "load_weights", "parse_config_dict", "register_architecture", "write_random_model",

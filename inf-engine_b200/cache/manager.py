@@ -33,7 +33,10 @@ class CacheRequirement:
     kind "kv": pages of keys and values, ``n_kv_heads`` x ``head_dim`` per token
     (values ``v_head_dim`` a head when that is given), all of them (``window`` None)
     or the last ``window``.
+    With a window, ``keep_first`` keys at the start of the sequence stay as well (their pages are never given back).
     kind "state": one tensor of ``state_shape``/``state_dtype`` per request.
+    kind "several": a run that keeps more than one thing (pages beside a state, two states): ``parts`` lists them,
+    and the run's binding and view carry one entry per part, in that order.
     kind "none": nothing.
     """
 
@@ -45,6 +48,8 @@ class CacheRequirement:
     state_shape: tuple[int, ...] = ()
     state_dtype: torch.dtype | None = None
     v_head_dim: int | None = None
+    keep_first: int = 0
+    parts: tuple = ()
 
     @property
     def value_dim(self) -> int:
@@ -52,7 +57,8 @@ class CacheRequirement:
 
     def group_key(self):
         if self.kind == "kv":
-            return ("kv", self.n_kv_heads, self.head_dim, self.value_dim, self.window, self.dtype)
+            return ("kv", self.n_kv_heads, self.head_dim, self.value_dim, self.window, self.dtype,
+                    self.keep_first if self.window is not None else 0)
         if self.kind == "state":
             return ("state", self.state_shape, self.state_dtype)
         return ("none",)
@@ -72,6 +78,7 @@ class KVGroup:
     k: torch.Tensor | None = None            # [len(entries), n_pages, n_kv_heads, page_size, head_dim]
     v: torch.Tensor | None = None            # the same with v_head_dim as its last size
     v_head_dim: int = 0                      # 0: as head_dim
+    keep_first: int = 0                      # with a window: this many first keys of a sequence stay
 
     @property
     def value_dim(self) -> int:
@@ -96,6 +103,7 @@ class CacheBinding:
     kind: str
     group: int = -1
     row: int = -1
+    parts: tuple = ()          # kind "several": one binding per part
 
 
 class CacheManager:
@@ -111,28 +119,34 @@ class CacheManager:
         self.state_groups: list[StateGroup] = []
         self.bindings: list[CacheBinding] = []
         keys: dict = {}
-        for entry, req in enumerate(requirements):
+
+        def bind(entry: int, req: CacheRequirement) -> CacheBinding:
             key = req.group_key()
             if req.kind == "kv":
                 if key not in keys:
                     keys[key] = len(self.kv_groups)
                     self.kv_groups.append(KVGroup(len(self.kv_groups), req.n_kv_heads, req.head_dim, req.window,
-                                                  req.dtype, [], PagePool(n_pages), v_head_dim=req.value_dim))
+                                                  req.dtype, [], PagePool(n_pages), v_head_dim=req.value_dim,
+                                                  keep_first=req.keep_first if req.window is not None else 0))
                 g = self.kv_groups[keys[key]]
                 g.entries.append(entry)
-                self.bindings.append(CacheBinding("kv", g.index, len(g.entries) - 1))
-            elif req.kind == "state":
+                return CacheBinding("kv", g.index, len(g.entries) - 1)
+            if req.kind == "state":
                 if key not in keys:
                     keys[key] = len(self.state_groups)
                     self.state_groups.append(StateGroup(len(self.state_groups), tuple(req.state_shape),
                                                         req.state_dtype, []))
                 g = self.state_groups[keys[key]]
                 g.entries.append(entry)
-                self.bindings.append(CacheBinding("state", g.index, len(g.entries) - 1))
-            elif req.kind == "none":
-                self.bindings.append(CacheBinding("none"))
-            else:
-                raise ValueError(f"unknown cache kind {req.kind!r}")
+                return CacheBinding("state", g.index, len(g.entries) - 1)
+            if req.kind == "several":
+                return CacheBinding("several", parts=tuple(bind(entry, part) for part in req.parts))
+            if req.kind == "none":
+                return CacheBinding("none")
+            raise ValueError(f"unknown cache kind {req.kind!r}")
+
+        for entry, req in enumerate(requirements):
+            self.bindings.append(bind(entry, req))
         self._free_slots = list(range(max_requests - 1, -1, -1))
         self.slots: dict = {}        # request id -> state slot
         self.lengths: dict = {}      # request id -> tokens held
@@ -228,7 +242,8 @@ class CacheManager:
                 continue
             first = self._first_needed_page(g, new_length)
             table = g.tables[rid]
-            lo = g.first_live[rid]
+            # pages that hold kept first keys are never given back: the frontier starts behind them
+            lo = max(g.first_live[rid], -(-g.keep_first // self.page_size))
             if first > lo:
                 self._give_back(g, [p for p in table[lo:first] if p >= 0])
                 for i in range(lo, min(first, len(table))):

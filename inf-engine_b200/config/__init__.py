@@ -1,4 +1,5 @@
 from .barerax import BareraxConfig
+from .kipezen import KipezenConfig
 from .llama import ConfigError, LlamaConfig
 from .registry import (
     ARCHITECTURES,
@@ -16,14 +17,19 @@ from .spec import (
     BigramDecoderSpec,
     BlockSpec,
     FeedForwardSpec,
+    GatedDeltaSpec,
+    GatedLinearRecurrenceSpec,
     GatedMLPSpec,
     GeneralDeltaSpec,
     HeadNormSpec,
     MixerSpec,
     ModelSpec,
     NormSpec,
+    ParallelMixerSpec,
     PolyNormMLPSpec,
     PositionSpec,
     RopeScaling,
+    RoutedExpertsSpec,
     ScheduleEntry,
+    ShortConvSpec,
 )

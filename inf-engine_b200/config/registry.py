@@ -106,3 +106,11 @@ def _barerax(d: dict, tensor_shapes: dict | None = None):
 
 
 register_architecture("Barerax", _barerax, reads_shapes=True)
+
+
+def _kipezen(d: dict):
+    from .kipezen import KipezenConfig
+    return KipezenConfig.from_dict(d)
+
+
+register_architecture("Kipezen", _kipezen)

@@ -15,7 +15,9 @@
 // (position encodings that bias scores by how far back a key lies).  An optional
 // float32 multiplier per query head scales the score before that term is added
 // (a learned temperature of each head), and values may have another head size
-// than queries and keys (hd_v; the pools are laid out with their own sizes).
+// than queries and keys (hd_v; the pools are laid out with their own sizes).  Beside a window the first
+// `keep_first` keys of the sequence may stay visible to every later query, at their true positions, and the
+// output may take a multiplier (a mixer that is one of several summed side by side).
 //
 // Work split: a block takes one (request, kv head) and a tile of 32
 // (token, head-in-group) pairs, so the `group` query heads that share a kv head
@@ -47,6 +49,8 @@ struct AttnGeneralParams {
   int bias_dists;
   const float* head_scale;  // [n_heads] or null: the score is scale * head_scale[head] * (q . k)
   int hd_v;                 // head size of the values and of the output
+  int keep_first;           // beside a window: keys at positions below this stay visible to every later query
+  float out_scale;          // multiplier of the output
 };
 
 template <typename T>
@@ -108,6 +112,9 @@ __global__ void __launch_bounds__(AG_THREADS) attention_general_kernel(AttnGener
     key_begin = max(0, ctx + first_t - p.window + 1);
     key_begin = (key_begin / AG_KEYS) * AG_KEYS;
   }
+  // with kept first keys the walk starts with their tiles and then jumps to the window's first tile
+  const int keep = p.window > 0 ? p.keep_first : 0;
+  const int keep_end = ((keep + AG_KEYS - 1) / AG_KEYS) * AG_KEYS;
 
   float acc[AG_MAX_ACC];
 #pragma unroll
@@ -115,7 +122,8 @@ __global__ void __launch_bounds__(AG_THREADS) attention_general_kernel(AttnGener
   float m_run = -INFINITY, l_run = 0.f;
   const int n_acc = (hdv + 7) >> 3;       // the last one of a value size that is no multiple of 8 is partly idle
 
-  for (int kt = key_begin; kt < key_end; kt += AG_KEYS) {
+  for (int kt = keep > 0 ? 0 : key_begin; kt < key_end; kt += AG_KEYS) {
+    if (kt >= keep_end && kt < key_begin) kt = key_begin;       // (both multiples of the tile)
     __syncthreads();  // previous tile fully consumed (and Qs staged, first time)
     for (int idx = tid; idx < AG_KEYS * hd; idx += AG_THREADS) {
       const int kk = idx / hd, d = idx - kk * hd;
@@ -152,7 +160,7 @@ __global__ void __launch_bounds__(AG_THREADS) attention_general_kernel(AttnGener
       const float* qr = Qs + row * ldq;
       const float* kr = Ks + kk * ldq;
       for (int d = 0; d < hd; ++d) dot += qr[d] * kr[d];
-      const bool visible = row_valid && kp <= my_limit && kp >= my_first;
+      const bool visible = row_valid && kp <= my_limit && (kp >= my_first || kp < keep);
       float sc = dot * my_scale;
       if (visible && my_bias != nullptr) sc += my_bias[min(my_limit - kp, p.bias_dists - 1)];
       s[jj] = visible ? sc : -INFINITY;
@@ -197,7 +205,7 @@ __global__ void __launch_bounds__(AG_THREADS) attention_general_kernel(AttnGener
   if (row_valid) {
     const int j = my_pair - my_t * group;
     T* o = (T*)p.out + (size_t)(q0 + my_t) * p.out_stride + (c * group + j) * hdv;
-    const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+    const float inv = l_run > 0.f ? p.out_scale / l_run : 0.f;
 #pragma unroll
     for (int i = 0; i < AG_MAX_ACC; ++i)
       if (i < n_acc && sub + 8 * i < hdv) o[sub + 8 * i] = from_f32<T>(acc[i] * inv);
@@ -209,7 +217,8 @@ extern "C" int ie_attention_general(const void* q, void* out, const void* kpool,
                                     const int* work_req, const int* work_pair0, int q_stride, int out_stride,
                                     int table_stride, int n_work, int n_heads, int n_kv_heads, int hd,
                                     int page_size, int window, float scale, int act_dtype, const float* score_bias,
-                                    int bias_dists, const float* head_scale, int hd_v, cudaStream_t stream) {
+                                    int bias_dists, const float* head_scale, int hd_v, int keep_first,
+                                    float out_scale, cudaStream_t stream) {
   if (n_work <= 0) return IE_OK;
   if (hd_v <= 0) hd_v = hd;
   if (hd <= 0 || hd > 8 * AG_MAX_ACC || hd_v > 8 * AG_MAX_ACC) return IE_BAD_SIZE;
@@ -221,7 +230,7 @@ extern "C" int ie_attention_general(const void* q, void* out, const void* kpool,
   p.q_stride = q_stride; p.out_stride = out_stride; p.table_stride = table_stride;
   p.n_work = n_work; p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.hd = hd; p.page_size = page_size;
   p.window = window; p.scale = scale; p.score_bias = score_bias; p.bias_dists = bias_dists;
-  p.head_scale = head_scale; p.hd_v = hd_v;
+  p.head_scale = head_scale; p.hd_v = hd_v; p.keep_first = keep_first > 0 ? keep_first : 0; p.out_scale = out_scale;
   const size_t smem = sizeof(float) * ((size_t)AG_ROWS * (hd + 1) + (size_t)AG_KEYS * (hd + 1) +
                                        (size_t)AG_KEYS * hd_v + (size_t)AG_ROWS * (AG_KEYS + 1));
   dim3 grid(n_work, n_kv_heads);

@@ -32,7 +32,8 @@ BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-r
 
 # name -> sources; the headers every library depends on
 LIBRARIES = {
-    "core": ["elementwise.cu", "rowwise.cu", "attention_general.cu", "gemm_simt.cu", "sampling.cu"],
+    "core": ["elementwise.cu", "rowwise.cu", "sequence.cu", "routed.cu", "attention_general.cu", "gemm_simt.cu",
+             "sampling.cu"],
 }
 HEADERS = ["common.cuh"]
 

@@ -16,9 +16,13 @@
 template <typename TA, typename TW, typename TC>
 __global__ void __launch_bounds__(GS_THREADS) gemm_simt_kernel(const TA* __restrict__ A, const TW* __restrict__ W,
                                                                 TC* __restrict__ C, int M, int N, int K, int lda,
-                                                                int ldw, int ldc) {
+                                                                int ldw, int ldc, long long a_batch, long long w_batch,
+                                                                long long c_batch) {
   pdl_trigger();
   pdl_wait();
+  A += (size_t)blockIdx.z * a_batch;      // a batch of independent products (blockIdx.z), each with its own offsets
+  W += (size_t)blockIdx.z * w_batch;
+  C += (size_t)blockIdx.z * c_batch;
   __shared__ float As[GS_BK][GS_BM + 4];
   __shared__ float Ws[GS_BK][GS_BN + 4];
   const int m0 = blockIdx.y * GS_BM, n0 = blockIdx.x * GS_BN;
@@ -68,10 +72,11 @@ __global__ void __launch_bounds__(GS_THREADS) gemm_simt_kernel(const TA* __restr
 
 template <typename TA, typename TW, typename TC>
 static int launch_gemm(const void* A, const void* W, void* C, int M, int N, int K, int lda, int ldw, int ldc,
-                       cudaStream_t stream) {
-  dim3 grid((N + GS_BN - 1) / GS_BN, (M + GS_BM - 1) / GS_BM);
+                       cudaStream_t stream, int batch = 1, long long a_batch = 0, long long w_batch = 0,
+                       long long c_batch = 0) {
+  dim3 grid((N + GS_BN - 1) / GS_BN, (M + GS_BM - 1) / GS_BM, batch);
   return launch_k(gemm_simt_kernel<TA, TW, TC>, grid, GS_THREADS, 0, stream, (const TA*)A, (const TW*)W, (TC*)C, M, N,
-                  K, lda, ldw, ldc);
+                  K, lda, ldw, ldc, a_batch, w_batch, c_batch);
 }
 
 extern "C" int ie_gemm_simt(const void* A, int a_dtype, const void* W, int w_dtype, void* C, int c_dtype, int M,
@@ -86,6 +91,24 @@ extern "C" int ie_gemm_simt(const void* A, int a_dtype, const void* W, int w_dty
     case 5: return launch_gemm<bf16, float, bf16>(A, W, C, M, N, K, lda, ldw, ldc, stream);
     case 6: return launch_gemm<bf16, bf16, float>(A, W, C, M, N, K, lda, ldw, ldc, stream);
     case 7: return launch_gemm<bf16, bf16, bf16>(A, W, C, M, N, K, lda, ldw, ldc, stream);
+    default: return IE_BAD_DTYPE;
+  }
+}
+
+// `batch` independent products in one launch: product b reads A + b * a_batch, W + b * w_batch and writes
+// C + b * c_batch (offsets in elements).  A block-diagonal matrix applied to the rows of A is such a batch: block b
+// reads columns b * K .. of A and writes columns b * N .. of C.
+extern "C" int ie_gemm_simt_batched(const void* A, int a_dtype, const void* W, int w_dtype, void* C, int c_dtype, int M,
+                                    int N, int K, int lda, int ldw, int ldc, int batch, long long a_batch,
+                                    long long w_batch, long long c_batch, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || batch <= 0) return IE_OK;
+  if (K <= 0 || batch > 65535) return IE_BAD_SIZE;
+  const int code = a_dtype * 4 + w_dtype * 2 + c_dtype;
+  switch (code) {
+    case 0: return launch_gemm<float, float, float>(A, W, C, M, N, K, lda, ldw, ldc, stream, batch, a_batch, w_batch, c_batch);
+    case 2: return launch_gemm<float, bf16, float>(A, W, C, M, N, K, lda, ldw, ldc, stream, batch, a_batch, w_batch, c_batch);
+    case 4: return launch_gemm<bf16, float, float>(A, W, C, M, N, K, lda, ldw, ldc, stream, batch, a_batch, w_batch, c_batch);
+    case 6: return launch_gemm<bf16, bf16, float>(A, W, C, M, N, K, lda, ldw, ldc, stream, batch, a_batch, w_batch, c_batch);
     default: return IE_BAD_DTYPE;
   }
 }

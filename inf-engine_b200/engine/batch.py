@@ -58,6 +58,10 @@ class StepContext:
         self.handover = None
         self.upcoming_norm = None
         self.norm_after_block = None
+        self.last_block = False
+        # the residual rows in the activation type, when a part has them at hand (a block that norms its sublayers'
+        # outputs hands them from one sublayer to the next); void as soon as the residual changes otherwise
+        self.residual_cast = None
 
     def attention_work(self, group: int, rows: int, more_than: int = 0):
         """Work list for attention kernels that tile (token, head-in-group) pairs

@@ -80,7 +80,7 @@ def core():
         lib.ie_residual_add.argtypes = [P, P, I, I, I, P]
         lib.ie_rope_kv_write.argtypes = [P, P, P, I, I, P, P, P, P, P, P, I, I, I, I, I, I, I, P]
         lib.ie_silu_mul.argtypes = [P, P, I, I, I, I, I, P]
-        lib.ie_attention_general.argtypes = [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, I, P, I, P]
+        lib.ie_attention_general.argtypes = [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, I, P, I, I, F, P]
         lib.ie_layernorm.argtypes = [P, P, P, P, I, P, I, P, I, I, F, P]
         lib.ie_embed_bigram.argtypes = [P, P, P, P, I, P, P, I, P, P, I, I, I, I, L, L, P]
         lib.ie_add_bias.argtypes = [P, I, P, I, I, I, I, P]
@@ -88,13 +88,26 @@ def core():
         lib.ie_polynorm.argtypes = [P, P, P, I, P, I, I, I, I, F, P]
         lib.ie_headnorm_kv_write.argtypes = [P, P, P, I, I, I, P, P, I, F, P, P, P, I, I, I, I, I, I, I, I, P]
         lib.ie_gemm_simt.argtypes = [P, I, P, I, P, I, I, I, I, I, I, I, P]
+        lib.ie_gemm_simt_batched.argtypes = [P, I, P, I, P, I, I, I, I, I, I, I, I, L, L, L, P]
+        lib.ie_cast_rows.argtypes = [P, P, I, I, I, P]
+        lib.ie_outnorm_accumulate.argtypes = [P, P, I, I, P, I, P, I, I, I, F, P]
+        lib.ie_causal_conv.argtypes = [P, I, P, P, I, P, L, P, I, P, P, I, I, I, I, I, I, P]
+        lib.ie_linear_recurrence.argtypes = [P, I, P, I, P, P, I, P, P, P, I, P, P, I, P, P, I, I, F, F, I, I, P]
+        lib.ie_rownorm_rotate_write.argtypes = [P, P, P, I, I, I, P, P, P, P, P, I, F, P, I, P, P, P, P, I, I, I, I, I, I, I, P]
+        lib.ie_moe_route.argtypes = [P, I, P, I, P, P, P, I, I, I, I, I, F, F, I, P]
+        lib.ie_moe_sort.argtypes = [P, I, I, I, P, P, I, P]
+        lib.ie_moe_gemm.argtypes = [P, I, P, I, P, I, P, P, I, I, I, I, I, L, I, I, I, I, P]
+        lib.ie_moe_combine.argtypes = [P, P, P, P, I, I, P, I, I, I, P]
+        lib.ie_moe_tile_rows.restype = c_int
         lib.ie_argmax.argtypes = [P, P, I, I, L, P]
         lib.ie_repetition_penalty.argtypes = [P, P, P, I, I, L, I, P]
         lib.ie_sample.argtypes = [P, P, P, I, I, L, P]
         for name in ("ie_embed_gather", "ie_rmsnorm", "ie_residual_add", "ie_rope_kv_write", "ie_silu_mul",
                      "ie_attention_general", "ie_gemm_simt", "ie_argmax", "ie_repetition_penalty", "ie_sample",
                      "ie_layernorm", "ie_embed_bigram", "ie_add_bias", "ie_tanh", "ie_polynorm",
-                     "ie_headnorm_kv_write"):
+                     "ie_headnorm_kv_write", "ie_gemm_simt_batched", "ie_cast_rows", "ie_outnorm_accumulate",
+                     "ie_causal_conv", "ie_linear_recurrence", "ie_rownorm_rotate_write", "ie_moe_route", "ie_moe_sort",
+                     "ie_moe_gemm", "ie_moe_combine"):
             getattr(lib, name).restype = c_int
         _core = lib
         _apply_check_limits()
@@ -249,11 +262,12 @@ def attention_general(q: torch.Tensor, out: torch.Tensor, kpool: torch.Tensor, v
                       work_req: torch.Tensor, work_pair0: torch.Tensor, n_work: int, n_heads: int,
                       n_kv_heads: int, head_dim: int, page_size: int, window: int | None, scale: float,
                       score_bias: torch.Tensor | None = None, head_scale: torch.Tensor | None = None,
-                      v_head_dim: int | None = None) -> None:
+                      v_head_dim: int | None = None, keep_first: int = 0, out_scale: float = 1.0) -> None:
     """Paged causal attention in float32 arithmetic.  ``score_bias`` (float32 [n_heads, D], contiguous) is added to
     the scaled score of a query at position p and a key at position j as ``score_bias[head, min(p - j, D - 1)]``.
     ``head_scale`` (float32 [n_heads]) multiplies the score of its head beside ``scale``.  ``v_head_dim``: head size of
-    the values and of ``out`` when it is not ``head_dim``."""
+    the values and of ``out`` when it is not ``head_dim``.  ``keep_first``: beside a window, keys at positions below it
+    stay visible to every later query.  ``out_scale`` multiplies the output."""
     assert q.stride(1) == 1 and out.stride(1) == 1 and kpool.dtype == q.dtype == out.dtype
     assert block_table.dtype == torch.int32 and block_table.stride(1) == 1
     if score_bias is not None:
@@ -266,7 +280,7 @@ def attention_general(q: torch.Tensor, out: torch.Tensor, kpool: torch.Tensor, v
                                        n_kv_heads, head_dim, page_size, int(window or 0), float(scale),
                                        dtype_code(q.dtype), _ptr(score_bias),
                                        score_bias.shape[1] if score_bias is not None else 0, _ptr(head_scale),
-                                       int(v_head_dim or head_dim), _stream()),
+                                       int(v_head_dim or head_dim), int(keep_first or 0), float(out_scale), _stream()),
            f"attention_general(head_dim={head_dim}, heads={n_heads}/{n_kv_heads})")
 
 
@@ -280,6 +294,164 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     _check(core().ie_gemm_simt(_ptr(a), dtype_code(a.dtype), _ptr(w), dtype_code(w.dtype), _ptr(out),
                                dtype_code(out.dtype), m, n, k, a.stride(0), w.stride(0), out.stride(0),
                                _stream()), f"gemm_simt({a.dtype},{w.dtype}->{out.dtype})")
+
+
+def gemm_simt_batched(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """A block-diagonal matrix applied to rows, float32 products and sums: ``w`` is [blocks, n, k] (rows are outputs),
+    ``a`` [m, blocks * k] and ``out`` float32 [m, blocks * n]; block b maps columns b*k.. of ``a`` to columns b*n.. of
+    ``out``."""
+    blocks, n, k = w.shape
+    m = a.shape[0]
+    assert a.shape[1] == blocks * k and out.shape == (m, blocks * n) and out.dtype is torch.float32
+    assert a.stride(1) == 1 and w.is_contiguous() and out.stride(1) == 1
+    _check(core().ie_gemm_simt_batched(_ptr(a), dtype_code(a.dtype), _ptr(w), dtype_code(w.dtype), _ptr(out), IE_F32, m, n,
+                                       k, a.stride(0), k, out.stride(0), blocks, k, n * k, n, _stream()),
+           f"gemm_simt_batched({a.dtype},{w.dtype}, blocks={blocks})")
+
+
+# ------------------------------------------------------------- norm on a sublayer's output, state along a sequence
+def cast_rows(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out = x (float32 rows) in out's type."""
+    assert x.dtype is torch.float32 and x.is_contiguous() and out.is_contiguous() and out.shape == x.shape
+    _check(core().ie_cast_rows(_ptr(x), _ptr(out), dtype_code(out.dtype), x.shape[0], x.shape[1], _stream()), "cast_rows")
+
+
+def outnorm_accumulate(residual: torch.Tensor, y: torch.Tensor, gain: torch.Tensor, eps: float,
+                       next_in: torch.Tensor | None = None) -> None:
+    """residual += y / sqrt(mean(y^2) + eps) * gain, row by row; ``next_in`` (optional, activation type) takes the new
+    residual rows."""
+    n, d = residual.shape
+    assert residual.dtype is torch.float32 and residual.is_contiguous() and y.shape == (n, d) and y.stride(1) == 1
+    assert gain.shape == (d,) and (next_in is None or (next_in.is_contiguous() and next_in.shape == (n, d)))
+    _check(core().ie_outnorm_accumulate(_ptr(residual), _ptr(y), dtype_code(y.dtype), y.stride(0), _ptr(gain),
+                                        dtype_code(gain.dtype), _ptr(next_in),
+                                        dtype_code(next_in.dtype) if next_in is not None else IE_BF16, n, d, float(eps),
+                                        _stream()), "outnorm_accumulate")
+
+
+CONV_MAX_TAPS = 16
+
+
+def causal_conv(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, state: torch.Tensor, out: torch.Tensor,
+                q_start: torch.Tensor, slots: torch.Tensor, n_requests: int, activation: str | None = None,
+                write_state: bool = True) -> None:
+    """A causal convolution per channel over each request's tokens of the step: ``out[t, c] = act(bias[c] + sum_j
+    weight[c, j] * x[t - (taps - 1 - j), c])``.  ``state`` [slots, taps - 1, channels] (activation type) holds every
+    request's last inputs, oldest first, and is moved on by the step's tokens (with ``write_state``)."""
+    n, channels = x.shape
+    taps = weight.shape[1]
+    assert weight.shape == (channels, taps) and weight.is_contiguous() and x.stride(1) == 1 and out.stride(1) == 1
+    assert out.shape == (n, channels) and out.dtype == x.dtype and state.dtype == x.dtype and state.stride(-1) == 1
+    assert state.shape[1:] == (max(taps - 1, 0), channels) and (taps == 1 or state.stride(1) == channels)
+    assert bias is None or (bias.shape == (channels,) and bias.dtype == weight.dtype)
+    assert out.data_ptr() != x.data_ptr(), "the convolution reads earlier rows of its input after writing its output"
+    _check(core().ie_causal_conv(_ptr(x), x.stride(0), _ptr(weight), _ptr(bias), dtype_code(weight.dtype), _ptr(state),
+                                 state.stride(0), _ptr(out), out.stride(0), _ptr(q_start), _ptr(slots), n_requests,
+                                 channels, taps, {None: 0, "silu": 1}[activation], 1 if write_state else 0,
+                                 dtype_code(x.dtype), _stream()), f"causal_conv(channels={channels}, taps={taps})")
+
+
+def linear_recurrence(u: torch.Tensor, y_pre: torch.Tensor, r_pre: torch.Tensor, i_pre: torch.Tensor,
+                      r_bias: torch.Tensor, i_bias: torch.Tensor, lam: torch.Tensor, state: torch.Tensor,
+                      out: torch.Tensor, q_start: torch.Tensor, slots: torch.Tensor, n_requests: int,
+                      decay_scale: float, out_scale: float = 1.0, write_state: bool = True) -> None:
+    """The real-gated linear recurrent unit over each request's tokens of the step, per channel: r = sigmoid(r_pre +
+    r_bias), i = sigmoid(i_pre + i_bias), a = exp(-decay_scale * r * softplus(lam)), S <- a S + sqrt(1 - a^2) i u,
+    out = out_scale * S * gelu_tanh(y_pre).  ``r_pre``/``i_pre`` float32 (columns of one buffer), ``state`` float32
+    [slots, width]."""
+    n, width = u.shape
+    assert u.stride(1) == 1 and y_pre.stride(1) == 1 and y_pre.dtype == u.dtype == out.dtype and out.stride(1) == 1
+    assert r_pre.dtype is torch.float32 and i_pre.dtype is torch.float32 and r_pre.stride(0) == i_pre.stride(0)
+    assert r_pre.stride(1) == 1 and i_pre.stride(1) == 1 and state.dtype is torch.float32 and state.is_contiguous()
+    assert state.shape[1:] == (width,) and r_bias.dtype == i_bias.dtype == lam.dtype
+    assert r_bias.shape == i_bias.shape == lam.shape == (width,)
+    _check(core().ie_linear_recurrence(_ptr(u), u.stride(0), _ptr(y_pre), y_pre.stride(0), _ptr(r_pre), _ptr(i_pre),
+                                       r_pre.stride(0), _ptr(r_bias), _ptr(i_bias), _ptr(lam), dtype_code(lam.dtype),
+                                       _ptr(state), _ptr(out), out.stride(0), _ptr(q_start), _ptr(slots), n_requests,
+                                       width, float(decay_scale), float(out_scale), 1 if write_state else 0,
+                                       dtype_code(u.dtype), _stream()), f"linear_recurrence(width={width})")
+
+
+def rownorm_rotate_write(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_bias, k_bias, v_bias, q_gain, k_gain,
+                         eps: float, inv_freq: torch.Tensor | None, rot_dims: int, positions: torch.Tensor,
+                         slot_mapping: torch.Tensor | None, kpool: torch.Tensor | None, vpool: torch.Tensor | None,
+                         n_heads: int, n_kv_heads: int, head_dim: int, v_head_dim: int, page_size: int) -> None:
+    """For every token: biases added to q, k, v; q and k divided by the root mean square of their WHOLE row and
+    multiplied by gains of the row's size; the first ``rot_dims`` dimensions of every head of q and k turned in
+    neighbouring pairs by position * inv_freq (float32 [rot_dims / 2]); q written back in place, k and v into their
+    page slots (if pools are given).  Any of the biases and gains may be None (all given ones of one type)."""
+    n = q.shape[0]
+    assert q.stride(1) == 1 and k.stride(1) == 1 and v.stride(1) == 1 and q.dtype == k.dtype == v.dtype
+    given = [t for t in (q_bias, k_bias, v_bias, q_gain, k_gain) if t is not None]
+    assert all(t.dtype == given[0].dtype and t.is_contiguous() for t in given)
+    assert inv_freq is None or (inv_freq.dtype is torch.float32 and inv_freq.numel() * 2 >= rot_dims)
+    _check(core().ie_rownorm_rotate_write(_ptr(q), _ptr(k), _ptr(v), q.stride(0), k.stride(0), v.stride(0), _ptr(q_bias),
+                                          _ptr(k_bias), _ptr(v_bias), _ptr(q_gain), _ptr(k_gain),
+                                          dtype_code(given[0].dtype) if given else IE_F32, float(eps), _ptr(inv_freq),
+                                          int(rot_dims), _ptr(positions), _ptr(slot_mapping), _ptr(kpool), _ptr(vpool), n,
+                                          n_heads, n_kv_heads, head_dim, v_head_dim, page_size, dtype_code(q.dtype),
+                                          _stream()), "rownorm_rotate_write")
+
+
+# ------------------------------------------------------------------ a mixture of experts
+def moe_tile_rows() -> int:
+    return int(core().ie_moe_tile_rows())
+
+
+def moe_max_tiles(n_pairs: int, n_experts: int) -> int:
+    """An upper bound of the row tiles that ``moe_sort`` makes of ``n_pairs`` pairs (no tile spans two experts)."""
+    return -(-n_pairs // moe_tile_rows()) + min(n_experts, n_pairs)
+
+
+def moe_route(logits: torch.Tensor, correction: torch.Tensor | None, ids: torch.Tensor, weights: torch.Tensor,
+              gate: torch.Tensor | None, n_experts: int, top: int, n_groups: int, keep_groups: int, route_scale: float,
+              weight_eps: float, gate_col: int = -1) -> None:
+    """Per token, from float32 router ``logits`` [n, >= n_experts]: the chosen experts ``ids`` int32 [n, top] and their
+    ``weights`` float32 [n, top]; ``gate`` float32 [n] = sigmoid(logits[:, gate_col]) (the shared expert's)."""
+    n = logits.shape[0]
+    assert logits.dtype is torch.float32 and logits.stride(1) == 1 and ids.dtype is torch.int32 and ids.is_contiguous()
+    assert weights.dtype is torch.float32 and weights.is_contiguous() and ids.shape == weights.shape == (n, top)
+    assert gate is None or (gate.dtype is torch.float32 and gate.shape == (n,))
+    _check(core().ie_moe_route(_ptr(logits), logits.stride(0), _ptr(correction),
+                               dtype_code(correction.dtype) if correction is not None else IE_F32, _ptr(ids),
+                               _ptr(weights), _ptr(gate), n, n_experts, top, n_groups, keep_groups, float(route_scale),
+                               float(weight_eps), int(gate_col), _stream()), f"moe_route(experts={n_experts}, top={top})")
+
+
+def moe_sort(ids: torch.Tensor, n_experts: int, sorted_pairs: torch.Tensor, tiles: torch.Tensor) -> None:
+    """Order the (token, choice) pairs by expert: ``sorted_pairs`` int32 [n_pairs], ``tiles`` int32 [max_tiles, 4] =
+    (expert, first position, rows, 0)."""
+    n_pairs = ids.numel()
+    assert sorted_pairs.dtype is torch.int32 and sorted_pairs.numel() >= n_pairs and tiles.dtype is torch.int32
+    assert tiles.is_contiguous() and tiles.shape[1] == 4 and tiles.shape[0] >= moe_max_tiles(n_pairs, n_experts)
+    _check(core().ie_moe_sort(_ptr(ids), n_pairs, n_experts, moe_tile_rows(), _ptr(sorted_pairs), _ptr(tiles),
+                              tiles.shape[0], _stream()), "moe_sort")
+
+
+def moe_gemm(a: torch.Tensor, w: torch.Tensor, c: torch.Tensor, sorted_pairs: torch.Tensor, tiles: torch.Tensor,
+             top: int, gather: bool, scatter: bool, epi: str = "store") -> None:
+    """The grouped product over the tiles of ``moe_sort``: ``w`` [experts, N, K]; ``gather``: a pair's row of ``a`` is
+    its token's (pair // top), else its sorted position; ``scatter``: its row of ``c`` is the pair's index, else its
+    sorted position; ``epi`` "silu_mul": w's rows alternate gate, up and c is N / 2 wide."""
+    _, n, k = w.shape
+    assert w.is_contiguous() and a.stride(1) == 1 and c.stride(1) == 1 and a.shape[1] == k
+    _check(core().ie_moe_gemm(_ptr(a), dtype_code(a.dtype), _ptr(w), dtype_code(w.dtype), _ptr(c), dtype_code(c.dtype),
+                              _ptr(sorted_pairs), _ptr(tiles), tiles.shape[0], n, k, a.stride(0), c.stride(0), n * k, top,
+                              1 if gather else 0, 1 if scatter else 0, {"store": 0, "silu_mul": 1}[epi], _stream()),
+           f"moe_gemm(n={n}, k={k}, {epi})")
+
+
+def moe_combine(y: torch.Tensor, weights: torch.Tensor, gate: torch.Tensor | None, shared_out: torch.Tensor | None,
+                out: torch.Tensor) -> None:
+    """out[t] = sum_r weights[t, r] * y[t * top + r] + gate[t] * shared_out[t]; ``y`` and ``out`` float32."""
+    n, top = weights.shape
+    d = out.shape[1]
+    assert y.dtype is torch.float32 and y.is_contiguous() and y.shape == (n * top, d) and out.dtype is torch.float32
+    assert out.is_contiguous() and (shared_out is None or shared_out.stride(1) == 1)
+    _check(core().ie_moe_combine(_ptr(y), _ptr(weights), _ptr(gate), _ptr(shared_out),
+                                 dtype_code(shared_out.dtype) if shared_out is not None else IE_F32,
+                                 shared_out.stride(0) if shared_out is not None else 0, _ptr(out), n, d, top, _stream()),
+           "moe_combine")
 
 
 # ---------------------------------------------------------------------- sampling
@@ -491,6 +663,51 @@ def delta_rule(r, k, v, a_pre, g, w_pre, a_bias, w_bias, out_gain, state, out, q
         1 if write_state else 0, dtype_code(r.dtype), _stream()), f"delta_rule(head_dim={head_dim}, heads={n_heads})")
 
 
+# ------------------------------------------------- gated delta rule (a recurrent mixer)
+_gated_delta: dict[tuple, object] = {}
+
+
+def gated_delta_library(head_dim: int, v_head_dim: int):
+    """The gated delta-rule kernel built for one pair of head sizes; compiled when first asked for."""
+    key = (int(head_dim), int(v_head_dim))
+    lib = _gated_delta.get(key)
+    if lib is None:
+        if not (1 <= key[0] <= 512 and 1 <= key[1] <= 1024):
+            raise KernelError(f"the gated delta-rule kernel takes key heads up to 512 and value heads up to 1024, not {key}")
+        defines = {"IE_GD_DK": key[0], "IE_GD_DV": key[1], **BUILD_DEFINES.get("gated_delta", {})}
+        lib = load_library(f"gated_delta_k{key[0]}_v{key[1]}", ["gated_delta.cu"], defines)
+        P, I, F = c_void_p, c_int, c_float
+        lib.ie_gated_delta.argtypes = [P, P, P, I, I, P, P, I, P, I, P, P, P, I, P, P, I, P, P, I, I, I, I, I, F, F, I, I, P]
+        lib.ie_gated_delta.restype = c_int
+        _gated_delta[key] = lib
+        _apply_check_limits()
+    return lib
+
+
+def gated_delta(q, k, v, b_pre, a_pre, gate, a_log, dt_bias, out_gain, state, out, q_start, slots, n_requests: int,
+                n_heads: int, n_kv_heads: int, head_dim: int, v_head_dim: int, key_eps: float, norm_eps: float,
+                write_state: bool = True) -> None:
+    """One step of the gated delta rule for every (request, head) of the batch.
+
+    ``q, k`` [n, kv_heads * head_dim] and ``v`` [n, heads * v_head_dim] (after their convolutions and SiLU), ``b_pre,
+    a_pre`` [n, heads], ``gate`` [n, heads * v_head_dim]: row-strided views in the activation type; ``a_log, dt_bias``
+    [heads] and ``out_gain`` [v_head_dim] of one type; ``state`` float32 [slots, heads, head_dim, v_head_dim], read and
+    (with ``write_state``) written at ``slots[request]``; ``out`` [n, heads * v_head_dim] in the activation type: the
+    normed, gated result for the output projection."""
+    for t in (q, k, v, b_pre, a_pre, gate, out):
+        assert t.dtype == q.dtype and t.stride(1) == 1
+    assert q.stride(0) == k.stride(0) and b_pre.stride(0) == a_pre.stride(0)
+    assert q.shape[1] == k.shape[1] == n_kv_heads * head_dim and v.shape[1] == gate.shape[1] == n_heads * v_head_dim
+    assert state.dtype is torch.float32 and state.is_contiguous() and state.shape[1:] == (n_heads, head_dim, v_head_dim)
+    assert a_log.dtype == dt_bias.dtype == out_gain.dtype and out_gain.shape == (v_head_dim,)
+    _check(gated_delta_library(head_dim, v_head_dim).ie_gated_delta(
+        _ptr(q), _ptr(k), _ptr(v), q.stride(0), v.stride(0), _ptr(b_pre), _ptr(a_pre), b_pre.stride(0), _ptr(gate),
+        gate.stride(0), _ptr(a_log), _ptr(dt_bias), _ptr(out_gain), dtype_code(a_log.dtype), _ptr(state), _ptr(out),
+        out.stride(0), _ptr(q_start), _ptr(slots), n_requests, n_heads, n_kv_heads, head_dim, v_head_dim, float(key_eps),
+        float(norm_eps), 1 if write_state else 0, dtype_code(q.dtype), _stream()),
+        f"gated_delta(head_dim={head_dim}, v_head_dim={v_head_dim}, heads={n_heads}/{n_kv_heads})")
+
+
 # ----------------------------------------------- weight-streaming product for few rows
 STREAM_MAX_ROWS = 64        # what the kernel takes
 STREAM_BEST_ROWS = 16       # beyond this the library product is faster (activations are re-read per block)
@@ -687,8 +904,9 @@ def attention_tcgen05(q, out, kpool, vpool, block_table, q_start, ctx_before, wo
 
 # ------------------------------------------------ a checks build: page ids, slots and token ids compared with limits
 # (the device has no sanitizer here: this is what stands in for one while debugging a cache manager or a new part)
-CHECK_LIBRARIES = ("core", "attn_mma", "attn_tcgen05", "delta_rule")
-CHECK_UNITS = ("elementwise", "rowwise", "attention_general", "attention_mma", "attention_tcgen05", "delta_rule")
+CHECK_LIBRARIES = ("core", "attn_mma", "attn_tcgen05", "delta_rule", "gated_delta")
+CHECK_UNITS = ("elementwise", "rowwise", "sequence", "attention_general", "attention_mma", "attention_tcgen05",
+               "delta_rule", "gated_delta")
 CHECK_CODES = {1: "page id", 2: "cache slot", 3: "token id"}
 _check_limits: tuple[int, int, int] | None = None
 

@@ -1,12 +1,14 @@
-from . import attention, block, delta_rule, feedforward, model, norms, positions  # noqa: F401  (register the built-in parts)
+from . import attention, block, delta_rule, feedforward, gated_delta, model, norms, positions, recurrence, routed  # noqa: F401  (register the built-in parts)
 from .attention import CacheView, PagedAttention
-from .block import PreNormBlock
+from .block import OutputNormBlock, PreNormBlock
 from .delta_rule import GeneralDeltaMixer
 from .feedforward import GatedMLP, PolyNormMLP
+from .gated_delta import GatedDeltaMixer
 from .linear import Linear
 from .model import BigramDecoderModel, DecoderModel
 from .norms import LayerNorm, RMSNorm
-from .positions import BucketedBias, NoPosition, Rotary, distance_bucket, rotary_inv_freq, rotary_tables
+from .positions import BucketedBias, NoPosition, Rotary, RotaryPairs, distance_bucket, rotary_inv_freq, rotary_tables
+from .recurrence import GatedLinearRecurrence, ParallelMixer
 from .registry import (
     BLOCKS,
     FEEDFORWARDS,
@@ -22,4 +24,5 @@ from .registry import (
     register_norm,
     register_position,
 )
+from .routed import RoutedExperts
 from .runtime import Runtime, Staging, Workspace

@@ -15,6 +15,15 @@ each head's scores (``head_scale``), a bias by distance from the position
 encoding, and values of another head size than queries and keys
 (``v_head_dim``).  A layer that uses one of them runs the general kernel, which
 computes scores and weights in float32; the tensor-core kernels take none.
+
+Further options: biases of the three projections, an RMS norm over the WHOLE q
+row and k row (all heads at once) with gains of the row's size, a rotation of
+neighbouring pairs of each head's first dimensions with angles worked out from
+the position (``rotary_pairs``), keys at the start of the sequence that stay
+visible beside a window (``keep_first``), and a multiplier of the output
+(``out_scale``, for a mixer that is one of several summed side by side).  One
+kernel adds the biases, norms, rotates and writes the cache
+(``rownorm_rotate_write``); the general attention kernel takes the rest.
 """
 
 from __future__ import annotations
@@ -40,6 +49,7 @@ class CacheView:
     v: torch.Tensor | None = None
     state: torch.Tensor | None = None       # [max_requests, *state_shape]
     write: bool = True                      # False: this run reads another run's cache
+    parts: list | None = None               # kind "several": one view per part of the run's requirement
 
 
 @register_mixer("attention")
@@ -53,10 +63,18 @@ class PagedAttention:
             spec.k_proj: ExpectedTensor((spec.n_kv_heads * spec.head_dim, spec.hidden)),
             spec.v_proj: ExpectedTensor((spec.n_kv_heads * spec.value_dim, spec.hidden)),
         }
+        for name, width in ((spec.q_bias, spec.n_heads * spec.head_dim), (spec.k_bias, spec.n_kv_heads * spec.head_dim),
+                            (spec.v_bias, spec.n_kv_heads * spec.value_dim)):
+            if name is not None:
+                out[name] = ExpectedTensor((width,))
         if spec.qk_norm is not None:
             for name in (spec.qk_norm.q_weight, spec.qk_norm.k_weight):
                 if name is not None:
                     out[name] = ExpectedTensor((spec.head_dim,), init="gain")
+        if spec.q_row_norm is not None:
+            out[spec.q_row_norm] = ExpectedTensor((spec.n_heads * spec.head_dim,), init="gain")
+        if spec.k_row_norm is not None:
+            out[spec.k_row_norm] = ExpectedTensor((spec.n_kv_heads * spec.head_dim,), init="gain")
         out.update(position_class(spec.position).expected_tensors(spec.position))
         if spec.head_scale is not None:
             out[spec.head_scale] = ExpectedTensor((spec.n_heads,), init="gain")
@@ -75,7 +93,8 @@ class PagedAttention:
         ws = [tensors[spec.q_proj], tensors[spec.k_proj], tensors[spec.v_proj]]
         dtype = torch.float32 if any(w.dtype is torch.float32 for w in ws) else ws[0].dtype
         self.qkv = Linear(torch.cat([w.to(dtype) for w in ws], dim=0).contiguous(), rt, "qkv")
-        self.o = Linear(tensors[spec.o_proj], rt, "o")
+        self.o_weight = tensors[spec.o_proj]
+        self.o = Linear(self.o_weight, rt, "o")
         self.position = build_position(spec.position, tensors, rt)
         self.scale = float(spec.scale) if spec.scale is not None else float(spec.head_dim) ** -0.5
         self.v_dim = spec.value_dim
@@ -90,13 +109,29 @@ class PagedAttention:
         if self.q_gain is not None and self.k_gain is not None and self.q_gain.dtype != self.k_gain.dtype:
             self.q_gain, self.k_gain = self.q_gain.float(), self.k_gain.float()
         self.head_scale = tensors[spec.head_scale].float().contiguous() if spec.head_scale is not None else None
+        # biases, whole-row norms and the pair rotation ride in one kernel before the attention
+        self.pair_rotation = getattr(self.position, "pair_rotation", None)        # (inv_freq, rot_dims) or None
+        rowwise = [tensors[n] for n in (spec.q_bias, spec.k_bias, spec.v_bias, spec.q_row_norm, spec.k_row_norm) if n is not None]
+        self.row_mode = bool(rowwise) or self.pair_rotation is not None
+        if self.row_mode:
+            if qn is not None:
+                raise NotImplementedError("norms per head together with whole-row norms or biases are not built")
+            rdtype = torch.float32 if any(t.dtype is torch.float32 for t in rowwise) else (rowwise[0].dtype if rowwise else torch.float32)
+            pick = lambda n: tensors[n].to(rdtype).contiguous() if n is not None else None
+            self.q_bias, self.k_bias, self.v_bias = pick(spec.q_bias), pick(spec.k_bias), pick(spec.v_bias)
+            self.q_row_gain, self.k_row_gain = pick(spec.q_row_norm), pick(spec.k_row_norm)
+        self.keep_first = int(spec.keep_first) if spec.window is not None else 0
+        self.out_scale = float(spec.out_scale)
+        self.core_width = self.out_width
         # the tensor-core kernels and the fused decode kernel know none of these; such a layer runs the general kernel
-        self.plain = qn is None and self.head_scale is None and self.v_dim == spec.head_dim
+        self.plain = (qn is None and self.head_scale is None and self.v_dim == spec.head_dim and not self.row_mode
+                      and not self.keep_first and self.out_scale == 1.0)
 
     def cache_requirement(self) -> CacheRequirement:
         s = self.spec
         return CacheRequirement(kind="kv", n_kv_heads=s.n_kv_heads, head_dim=s.head_dim, window=s.window,
-                                dtype=self.rt.act_dtype, v_head_dim=None if self.v_dim == s.head_dim else self.v_dim)
+                                dtype=self.rt.act_dtype, v_head_dim=None if self.v_dim == s.head_dim else self.v_dim,
+                                keep_first=self.keep_first)
 
     def can_fuse(self, n_tokens: int, norm) -> bool:
         return hasattr(norm, "fusable_rms") and self.qkv.streams(n_tokens, normed=True) and self.o.streams(n_tokens)
@@ -118,7 +153,15 @@ class PagedAttention:
         out = self._rotate_write_attend(qkv, ctx, cache)
         return self.o(out, rt.ws.take("mixer_out", (n, s.hidden), rt.act_dtype))
 
-    def _rotate_write_attend(self, qkv: torch.Tensor, ctx, cache: CacheView) -> torch.Tensor:
+    def forward_core(self, x: torch.Tensor, ctx, cache: CacheView, out: torch.Tensor) -> None:
+        """``out`` ([n, heads * value size], may be a column slice) = the heads' outputs times ``out_scale``: what goes
+        into the output projection (a mixer that runs several side by side multiplies them all at once)."""
+        rt = self.rt
+        n = x.shape[0]
+        qkv = self.qkv(x, rt.ws.take("attn_qkv", (n, self.q_width + self.k_width + self.v_width), rt.act_dtype))
+        self._rotate_write_attend(qkv, ctx, cache, out)
+
+    def _rotate_write_attend(self, qkv: torch.Tensor, ctx, cache: CacheView, out: torch.Tensor | None = None) -> torch.Tensor:
         s, rt = self.spec, self.rt
         n = qkv.shape[0]
         q = qkv[:, :self.q_width]
@@ -129,7 +172,18 @@ class PagedAttention:
         # a position encoding may bias the scores by distance (float32 [n_heads, D]); only the general kernel takes it
         bias_of = getattr(self.position, "score_bias", None)
         bias = bias_of() if bias_of is not None else None
-        out = rt.ws.take("attn_out", (n, self.out_width), rt.act_dtype)
+        if out is None:
+            out = rt.ws.take("attn_out", (n, self.out_width), rt.act_dtype)
+        if self.row_mode:
+            if tables is not None:
+                raise NotImplementedError("a table rotation together with whole-row norms or biases is not built")
+            inv_freq, rot_dims = self.pair_rotation if self.pair_rotation is not None else (None, 0)
+            kpool, vpool = (cache.k, cache.v) if cache.write else (None, None)
+            kernels.rownorm_rotate_write(q, k, v, self.q_bias, self.k_bias, self.v_bias, self.q_row_gain, self.k_row_gain,
+                                         s.row_norm_eps, inv_freq, rot_dims, ctx.positions, kvctx.slot_mapping, kpool,
+                                         vpool, s.n_heads, s.n_kv_heads, s.head_dim, self.v_dim, ctx.page_size)
+            self._attend(q, out, cache, ctx, kvctx, bias=bias, head_scale=self.head_scale)
+            return out
         if not self.plain:
             return self._attend_general(q, k, v, out, ctx, cache, kvctx, tables, bias)
         if (tables is not None and bias is None and ctx.max_q_len == 1 and ctx.n_tokens == ctx.n_requests
@@ -211,7 +265,7 @@ class PagedAttention:
         # a bias by distance or a multiplier per head: the bias build of the mma.sync kernels (scores, maxima and
         # sums in float32, weights to two bfloat16 terms); the tcgen05 kernel has no such input
         if (self.rt.act_dtype is torch.bfloat16 and s.head_dim in kernels.MMA_HEAD_DIMS and self.v_dim == s.head_dim
-                and (not extras or group <= 16)):
+                and (not extras or group <= 16) and not self.keep_first and self.out_scale == 1.0 and not self.row_mode):
             extra = dict(score_bias_log2e=self._bias_log2e(bias), head_scale=head_scale) if extras else {}
             # tensor-core kernels, built for this head size when first used
             n_small, small_keys = (ctx.n_requests, ctx.keys_cap) if ctx.max_q_len * group <= 16 \
@@ -250,7 +304,8 @@ class PagedAttention:
         work_req, work_pair0, n_work = ctx.attention_work(group, 32)
         kernels.attention_general(q, out, cache.k, cache.v, kvctx.block_table, ctx.q_start, ctx.ctx_before,
                                   work_req, work_pair0, n_work, s.n_heads, s.n_kv_heads, s.head_dim,
-                                  ctx.page_size, s.window, self.scale, bias, head_scale, self.v_dim)
+                                  ctx.page_size, s.window, self.scale, bias, head_scale, self.v_dim, self.keep_first,
+                                  self.out_scale)
 
 
 # fewer (token, head-in-group) rows than this in every request: the 64-row mma.sync tiles waste less

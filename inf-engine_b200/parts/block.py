@@ -44,6 +44,7 @@ class PreNormBlock:
 
     def forward(self, residual, pending, ctx, cache):
         n = ctx.n_tokens
+        ctx.residual_cast = None      # this block changes the residual without keeping a cast copy of it
         # a part may offer forward_fused(residual, norm, ...): it applies the norm and adds its own
         # result into the residual inside its kernels (worth it for the few rows of a decode step)
         # ctx.upcoming_norm tells a fused part which norm follows its product into the residual (it may prepare
@@ -78,6 +79,65 @@ class PreNormBlock:
         h = self.ff_norm.add_norm(residual, a)
         m = self.feedforward.forward(h, ctx)
         return residual, m
+
+
+@register_block("outnorm")
+class OutputNormBlock:
+    """``x += norm1(mixer(x)); x += norm2(ff(x))``: the sublayers read the residual stream itself and the norm sits
+    on what they return.  The residual is float32; a sublayer's input is its rows in the activation type (the
+    residual itself on the 32-bit path), which the norm kernel of the sublayer before leaves behind as it adds."""
+
+    @staticmethod
+    def expected_tensors(spec):
+        return PreNormBlock.expected_tensors(spec)
+
+    def __init__(self, spec, tensors, rt):
+        self.spec = spec
+        self.rt = rt
+        self.mixer_norm = build_norm(spec.mixer_norm, tensors, rt)
+        self.mixer = build_mixer(spec.mixer, tensors, rt)
+        self.ff_norm = build_norm(spec.ff_norm, tensors, rt) if spec.feedforward is not None else None
+        self.feedforward = build_feedforward(spec.feedforward, tensors, rt) if spec.feedforward is not None else None
+        for norm in (self.mixer_norm, self.ff_norm):
+            if norm is not None and not hasattr(norm, "accumulate"):
+                raise ValueError(f"a block that norms its sublayers' outputs needs a norm with accumulate(); "
+                                 f"{type(norm).__name__} has none")
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(getattr(p, "graph_safe", False) for p in (self.mixer, self.feedforward) if p is not None)
+
+    def _input(self, residual, ctx):
+        """The residual rows as a sublayer reads them."""
+        if self.rt.exact:
+            return residual
+        if ctx.residual_cast is None:
+            ctx.residual_cast = self.rt.ws.take("block_in", tuple(residual.shape), self.rt.act_dtype)
+            kernels.cast_rows(residual, ctx.residual_cast)
+        return ctx.residual_cast
+
+    def _next_input(self, residual, wanted: bool):
+        if self.rt.exact or not wanted:
+            return None
+        return self.rt.ws.take("block_in", tuple(residual.shape), self.rt.act_dtype)
+
+    def forward(self, residual, pending, ctx, cache):
+        ctx.handover = None
+        ctx.upcoming_norm = None
+        if pending is not None:
+            kernels.residual_add(residual, pending)
+            ctx.residual_cast = None
+        a = self.mixer.forward(self._input(residual, ctx), ctx, cache)
+        last = getattr(ctx, "last_block", False)
+        nxt = self._next_input(residual, self.feedforward is not None or not last)
+        self.mixer_norm.accumulate(residual, a, nxt)
+        ctx.residual_cast = nxt
+        if self.feedforward is not None:
+            m = self.feedforward.forward(self._input(residual, ctx), ctx)
+            nxt = self._next_input(residual, not last)
+            self.ff_norm.accumulate(residual, m, nxt)
+            ctx.residual_cast = nxt
+        return residual, None
 
 
 def _fuses(part, n_tokens: int, norm) -> bool:

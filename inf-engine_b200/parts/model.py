@@ -58,18 +58,21 @@ class DecoderModel:
         return reqs
 
     def bind_cache(self, manager: CacheManager) -> None:
+        def view(b, write: bool) -> CacheView:
+            if b.kind == "kv":
+                g = manager.kv_groups[b.group]
+                return CacheView("kv", b.group, g.k[b.row], g.v[b.row], None, write=write)
+            if b.kind == "state":
+                g = manager.state_groups[b.group]
+                return CacheView("state", b.group, None, None, g.data[b.row], write=write)
+            if b.kind == "several":
+                return CacheView("several", write=write, parts=[view(part, write) for part in b.parts])
+            return CacheView("none")
+
         views = []
         for i, e in enumerate(self.spec.schedule):
             src = i if e.cache_from is None else e.cache_from
-            b = manager.bindings[src]
-            if b.kind == "kv":
-                g = manager.kv_groups[b.group]
-                views.append(CacheView("kv", b.group, g.k[b.row], g.v[b.row], None, write=e.cache_from is None))
-            elif b.kind == "state":
-                g = manager.state_groups[b.group]
-                views.append(CacheView("state", b.group, None, None, g.data[b.row], write=e.cache_from is None))
-            else:
-                views.append(CacheView("none"))
+            views.append(view(manager.bindings[src], e.cache_from is None))
         self._views = views
 
     # ---------------------------------------------------------------- forward
@@ -92,11 +95,13 @@ class DecoderModel:
         residual = self.embed(ctx)
         pending = None
         ctx.handover = None
+        ctx.residual_cast = None
         last = len(spec.schedule) - 1
         for i, e in enumerate(spec.schedule):
             # the norm that the residual meets after this block: the next block's first, or the final one
             nxt = self.layers[spec.schedule[i + 1].layer] if i < last else None
             ctx.norm_after_block = getattr(nxt, "mixer_norm", None) if nxt is not None else self.final_norm
+            ctx.last_block = i == last
             residual, pending = self.layers[e.layer].forward(residual, pending, ctx, self._views[i])
         ctx.norm_after_block = None
         m = ctx.n_logits

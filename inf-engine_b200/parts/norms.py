@@ -1,6 +1,9 @@
 """RMSNorm: ``x / sqrt(mean(x^2) + eps) * gain`` (engine/layers.py:11-25), with
 float32 statistics whatever the activation dtype, fused with the residual sum
-that precedes it in a pre-norm block (engine/llama_block.py:53-62).
+that precedes it in a pre-norm block (engine/llama_block.py:53-62).  With
+``unit_offset`` the stored tensor lies around zero and the gain is one plus it
+(formed once, in float32).  ``accumulate`` is the norm of a block that norms its
+sublayers' OUTPUTS: the normed rows are added into the residual.
 LayerNorm: ``(x - mean) / sqrt(variance + eps) * weight + bias`` with the variance
 the mean of the squared deviations, the same way."""
 
@@ -23,8 +26,14 @@ class RMSNorm:
         self.spec = spec
         self.rt = rt
         self.gain = tensors[spec.weight]
+        if getattr(spec, "unit_offset", False):
+            self.gain = (1.0 + self.gain.float()).contiguous()
         self.eps = float(spec.eps)
         self.size = spec.size
+
+    def accumulate(self, residual: torch.Tensor, y: torch.Tensor, next_in: torch.Tensor | None = None) -> None:
+        """residual += norm(y); ``next_in`` (activation type, optional) takes the new residual rows."""
+        kernels.outnorm_accumulate(residual, y, self.gain, self.eps, next_in)
 
     def fusable_rms(self):
         """(gain, eps) for kernels that apply this norm inside a matrix product's prologue."""

@@ -83,6 +83,35 @@ class Rotary:
         return None
 
 
+@register_position("rotary_pairs")
+class RotaryPairs:
+    """Neighbouring dimensions (2i, 2i + 1) of the first ``rot_dims`` dimensions of every head turn by the angle
+    ``position * theta^(-2i / rot_dims)``; the other dimensions pass unchanged.  There is no table: the kernel that
+    norms q and k and writes the cache forms the angle in float32 from the position and these frequencies (worked
+    out here in float64 and rounded once), so positions have no limit."""
+
+    @staticmethod
+    def expected_tensors(spec):
+        return {}
+
+    def __init__(self, spec, tensors, rt):
+        if spec.rot_dims % 2 or not 0 < spec.rot_dims <= spec.head_dim:
+            raise ValueError(f"pair rotation needs an even number of dimensions up to the head's {spec.head_dim}, not {spec.rot_dims}")
+        self.spec = spec
+        key = ("rotary_pairs", spec.theta, spec.rot_dims)
+        if key not in rt.shared:
+            i = torch.arange(spec.rot_dims // 2, dtype=torch.float64)
+            rt.shared[key] = (float(spec.theta) ** (-2.0 * i / spec.rot_dims)).float().to(rt.device)
+        self.inv_freq = rt.shared[key]
+        self.pair_rotation = (self.inv_freq, spec.rot_dims)
+
+    def rotary_tables(self):
+        return None
+
+    def rotate(self, q, k, ctx):
+        return None
+
+
 def distance_bucket(n: int, n_buckets: int, max_distance: int) -> int:
     """Row of a bucketed distance table for a key that lies ``n`` positions back.
 
