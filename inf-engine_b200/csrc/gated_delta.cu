@@ -45,7 +45,7 @@ constexpr int gd_pick_ks() {
 
 static_assert(GD_DK >= 1 && GD_DV >= 1 && GD_DV <= 1024, "value heads up to 1024 channels: one block a head");
 static_assert(GD_DKP <= 128, "a thread keeps its rows of a state column in registers");
-static_assert(GD_TT * (2 * GD_ROW + 3 * GD_DV + 2) * 4 <= 48 * 1024, "a tile's vectors must fit in shared memory");
+static_assert(GD_TT * (2 * GD_ROW + 3 * GD_DV + 3) * 4 <= 48 * 1024, "a tile's vectors must fit in shared memory");
 
 struct GatedDeltaParams {
   const void* q;            // activation type, [N, *_stride]: columns of one buffer (after convolution and SiLU)
@@ -80,7 +80,7 @@ __device__ __forceinline__ float gd_column_sum(float v) {
 template <typename TA, typename TW>
 __global__ void __launch_bounds__(GD_THREADS) gated_delta_kernel(GatedDeltaParams p) {
   __shared__ __align__(16) float sq[GD_TT][GD_ROW], sk[GD_TT][GD_ROW];
-  __shared__ float sv[GD_TT][GD_DV], sg[GD_TT][GD_DV], so[GD_TT][GD_DV], sbeta[GD_TT], sdecay[GD_TT];
+  __shared__ float sv[GD_TT][GD_DV], sg[GD_TT][GD_DV], so[GD_TT][GD_DV], sbeta[GD_TT], sdecay[GD_TT], sdecm1[GD_TT];
   pdl_trigger();
   pdl_wait();
   const int req = blockIdx.x, h = blockIdx.y;
@@ -131,7 +131,11 @@ __global__ void __launch_bounds__(GD_THREADS) gated_delta_kernel(GatedDeltaParam
       const float b = to_f32(((const TA*)p.b_pre)[(size_t)(t0 + tid) * p.ba_stride + h]);
       const float a = to_f32(((const TA*)p.a_pre)[(size_t)(t0 + tid) * p.ba_stride + h]) + dt_bias;
       sbeta[tid] = 1.f / (1.f + expf(-b));
-      sdecay[tid] = expf(rate * (a > 20.f ? a : log1pf(expf(a))));
+      // the decay, and the decay less one when it is above one half: a float32 decay of 1 - 2.5e-6 is off by up to a
+      // hundredth of its distance from one, which a thousand tokens turn into the fifth digit of the state
+      const float log_g = rate * (a > 20.f ? a : log1pf(expf(a)));
+      sdecay[tid] = expf(log_g);
+      sdecm1[tid] = log_g > -0.6931472f ? expm1f(log_g) : 0.f;
     }
     __syncthreads();
     for (int tt = warp; tt < nt; tt += n_warps) {
@@ -166,14 +170,21 @@ __global__ void __launch_bounds__(GD_THREADS) gated_delta_kernel(GatedDeltaParam
         }
       }
       const float vj = active ? sv[tt][j] : 0.f;
-      const float g = sdecay[tt], beta = sbeta[tt];
+      const float g = sdecay[tt], gm1 = sdecm1[tt], beta = sbeta[tt];
       float ks[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < GD_DKP; ++i) ks[i & 3] = fmaf(kk[i], S[i], ks[i & 3]);
-      const float seen = g * gd_column_sum((ks[0] + ks[1]) + (ks[2] + ks[3]));     // (g S)^T k
-      const float u = beta * (vj - seen);
+      const float sk_old = gd_column_sum((ks[0] + ks[1]) + (ks[2] + ks[3]));
+      float u;
+      if (gm1 != 0.f) {                  // g S as S + (g - 1) S
+        u = beta * (vj - fmaf(gm1, sk_old, sk_old));                                // (g S)^T k
 #pragma unroll
-      for (int i = 0; i < GD_DKP; ++i) S[i] = fmaf(kk[i], u, g * S[i]);
+        for (int i = 0; i < GD_DKP; ++i) S[i] = fmaf(kk[i], u, fmaf(gm1, S[i], S[i]));
+      } else {
+        u = beta * (vj - g * sk_old);
+#pragma unroll
+        for (int i = 0; i < GD_DKP; ++i) S[i] = fmaf(kk[i], u, g * S[i]);
+      }
       float oo[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < GD_DKP; ++i) oo[i & 3] = fmaf(S[i], qq[i], oo[i & 3]);

@@ -180,13 +180,21 @@ extern "C" int ie_causal_conv(const void* x, int x_stride, const void* w, const 
 //     r = sigmoid(r_pre + r_bias),  i = sigmoid(i_pre + i_bias)             (r_pre, i_pre: float32 gate products)
 //     log a = -decay_scale * r * softplus(lam),  a = exp(log a)
 //     S <- a S + sqrt(1 - a^2) (i * u);    out = out_scale * S * gelu_tanh(y_pre)
-// 1 - a^2 is formed as -expm1(2 log a), which keeps its digits when a is close to one.  A thread owns a channel
+// 1 - a^2 is formed as -expm1(2 log a), which keeps its digits when a is close to one; and while a is above one
+// half the state is moved by S += (a - 1) S + input with a - 1 = expm1(log a): a float32 a = 1 - 2.5e-6 is off by up
+// to a hundredth of its distance from one, which over a thousand tokens shows in the fifth digit of S.  A thread owns a channel
 // of a request and walks the step's tokens in order; the loads of a token do not depend on S, so several
 // tokens' loads are in flight while the chain runs.
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
 __device__ __forceinline__ float gelu_tanh_f(float z) {
   return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+// S <- exp(log_a) S + in, log_a <= 0
+__device__ __forceinline__ float lru_step(float S, float log_a, float in) {
+  if (log_a > -0.6931472f) return S + fmaf(expm1f(log_a), S, in);
+  return fmaf(expf(log_a), S, in);
 }
 
 #define LRU_UNROLL 4
@@ -225,18 +233,16 @@ linear_recurrence_kernel(const TA* __restrict__ u, int u_stride, const TA* __res
 #pragma unroll
     for (int k = 0; k < LRU_UNROLL; ++k) {
       const float log_a = rate * sigmoid_f(rp[k] + rb);
-      const float a = expf(log_a);
       const float in = sqrtf(-expm1f(2.f * log_a)) * (sigmoid_f(ip[k] + ib) * uu[k]);
-      S = fmaf(a, S, in);
+      S = lru_step(S, log_a, in);
       out[(size_t)(t + k) * out_stride + c] = from_f32<TA>(out_scale * S * gelu_tanh_f(yy[k]));
     }
   }
   for (; t < q1; ++t) {
     const float log_a = rate * sigmoid_f(r_pre[(size_t)t * g_stride + c] + rb);
-    const float a = expf(log_a);
     const float in = sqrtf(-expm1f(2.f * log_a)) *
                      (sigmoid_f(i_pre[(size_t)t * g_stride + c] + ib) * to_f32(u[(size_t)t * u_stride + c]));
-    S = fmaf(a, S, in);
+    S = lru_step(S, log_a, in);
     out[(size_t)t * out_stride + c] =
         from_f32<TA>(out_scale * S * gelu_tanh_f(to_f32(y_pre[(size_t)t * y_stride + c])));
   }
@@ -267,7 +273,7 @@ extern "C" int ie_linear_recurrence(const void* u, int u_stride, const void* y_p
 // For every token: q <- q + q_bias, divided by the root mean square of the WHOLE row (all heads together; eps inside
 // the root) and multiplied by a gain of the row's size; the same for k; v <- v + v_bias.  Then, in every head of q
 // and k, the first rot_dims dimensions turn in neighbouring pairs: (a, b) at dimensions (2i, 2i + 1) becomes
-// (a cos - b sin, b cos + a sin) of the angle position * inv_freq[i], formed in float32 from the position.  q is
+// (a cos - b sin, b cos + a sin) of the angle position * inv_freq[i] (float64 frequencies).  q is
 // written back in place; k and v go to the token's place in the cache pages (and nowhere else).  A null gain or
 // bias leaves that step out.  One block per token; the normed rows are staged in shared memory.
 template <typename TA, typename TW>
@@ -275,7 +281,7 @@ __global__ void rownorm_rotate_write_kernel(TA* __restrict__ q, const TA* __rest
                                             int q_stride, int k_stride, int v_stride, const TW* __restrict__ q_bias,
                                             const TW* __restrict__ k_bias, const TW* __restrict__ v_bias,
                                             const TW* __restrict__ q_gain, const TW* __restrict__ k_gain, float eps,
-                                            const float* __restrict__ inv_freq, int rot_dims,
+                                            const double* __restrict__ inv_freq, int rot_dims,
                                             const int* __restrict__ positions, const int* __restrict__ slot_mapping,
                                             TA* __restrict__ kpool, TA* __restrict__ vpool, int n_heads,
                                             int n_kv_heads, int hd, int hd_v, int page_size) {
@@ -321,7 +327,15 @@ __global__ void rownorm_rotate_write_kernel(TA* __restrict__ q, const TA* __rest
     if (le < rot_dims) {
       const int pair = le >> 1;
       float sn, cs;
-      sincosf(pos * inv_freq[pair], &sn, &cs);
+#ifdef IE_ANGLE_F32
+      sincosf(pos * (float)inv_freq[pair], &sn, &cs);
+#else
+      // frequency times position is formed and brought into one turn in double, then the sine and cosine are float32:
+      // a float32 product at position 100,000 would be off by a thousandth of a radian before any sine is taken, and
+      // a frequency rounded to float32 puts a key 1,000 positions back off by 3e-5 of a radian
+      const double turns = (double)pos * inv_freq[pair] * 0.15915494309189535;
+      sincosf((float)((turns - floor(turns)) * 6.283185307179586), &sn, &cs);
+#endif
       const float a = src[h * hd + 2 * pair], b = src[h * hd + 2 * pair + 1];
       val = (le & 1) ? fmaf(b, cs, a * sn) : fmaf(a, cs, -b * sn);
     }
@@ -340,7 +354,7 @@ __global__ void rownorm_rotate_write_kernel(TA* __restrict__ q, const TA* __rest
 
 extern "C" int ie_rownorm_rotate_write(void* q, const void* k, const void* v, int q_stride, int k_stride, int v_stride,
                                        const void* q_bias, const void* k_bias, const void* v_bias, const void* q_gain,
-                                       const void* k_gain, int w_dtype, float eps, const float* inv_freq, int rot_dims,
+                                       const void* k_gain, int w_dtype, float eps, const double* inv_freq, int rot_dims,
                                        const int* positions, const int* slot_mapping, void* kpool, void* vpool,
                                        int n_tokens, int n_heads, int n_kv_heads, int hd, int hd_v, int page_size,
                                        int act_dtype, cudaStream_t stream) {

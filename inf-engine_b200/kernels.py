@@ -378,13 +378,13 @@ def rownorm_rotate_write(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_bi
                          n_heads: int, n_kv_heads: int, head_dim: int, v_head_dim: int, page_size: int) -> None:
     """For every token: biases added to q, k, v; q and k divided by the root mean square of their WHOLE row and
     multiplied by gains of the row's size; the first ``rot_dims`` dimensions of every head of q and k turned in
-    neighbouring pairs by position * inv_freq (float32 [rot_dims / 2]); q written back in place, k and v into their
+    neighbouring pairs by position * inv_freq (float64 [rot_dims / 2]); q written back in place, k and v into their
     page slots (if pools are given).  Any of the biases and gains may be None (all given ones of one type)."""
     n = q.shape[0]
     assert q.stride(1) == 1 and k.stride(1) == 1 and v.stride(1) == 1 and q.dtype == k.dtype == v.dtype
     given = [t for t in (q_bias, k_bias, v_bias, q_gain, k_gain) if t is not None]
     assert all(t.dtype == given[0].dtype and t.is_contiguous() for t in given)
-    assert inv_freq is None or (inv_freq.dtype is torch.float32 and inv_freq.numel() * 2 >= rot_dims)
+    assert inv_freq is None or (inv_freq.dtype is torch.float64 and inv_freq.is_contiguous() and inv_freq.numel() * 2 >= rot_dims)
     _check(core().ie_rownorm_rotate_write(_ptr(q), _ptr(k), _ptr(v), q.stride(0), k.stride(0), v.stride(0), _ptr(q_bias),
                                           _ptr(k_bias), _ptr(v_bias), _ptr(q_gain), _ptr(k_gain),
                                           dtype_code(given[0].dtype) if given else IE_F32, float(eps), _ptr(inv_freq),

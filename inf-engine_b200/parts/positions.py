@@ -87,8 +87,9 @@ class Rotary:
 class RotaryPairs:
     """Neighbouring dimensions (2i, 2i + 1) of the first ``rot_dims`` dimensions of every head turn by the angle
     ``position * theta^(-2i / rot_dims)``; the other dimensions pass unchanged.  There is no table: the kernel that
-    norms q and k and writes the cache forms the angle in float32 from the position and these frequencies (worked
-    out here in float64 and rounded once), so positions have no limit."""
+    norms q and k and writes the cache forms the angle from the position and these frequencies (float64, so that
+    neither a large position nor a key far back costs digits; sine and cosine are float32), and positions have no
+    limit."""
 
     @staticmethod
     def expected_tensors(spec):
@@ -101,7 +102,7 @@ class RotaryPairs:
         key = ("rotary_pairs", spec.theta, spec.rot_dims)
         if key not in rt.shared:
             i = torch.arange(spec.rot_dims // 2, dtype=torch.float64)
-            rt.shared[key] = (float(spec.theta) ** (-2.0 * i / spec.rot_dims)).float().to(rt.device)
+            rt.shared[key] = (float(spec.theta) ** (-2.0 * i / spec.rot_dims)).to(rt.device)
         self.inv_freq = rt.shared[key]
         self.pair_rotation = (self.inv_freq, spec.rot_dims)
 
