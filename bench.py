@@ -395,6 +395,25 @@ def _family_configs(size):
     return brx, llama
 
 
+def _kipezen_configs(size):
+    """A Kipezen model of the size's width (three delta layers to one parallel layer; 16 experts of which a token runs
+    two, and a shared one: as many ACTIVE feed-forward parameters as the dense models beside it) and the Barerax model
+    of equal width, depth and heads, the closest family the engine had."""
+    from inf_engine_b200.config import parse_config_dict
+    z = FAMILY_SIZES[size]
+    w, H, G, inter = z["width"], z["heads"], z["kv"], z["inter"]
+    mlp = {"kind": "moe", "expert": {"ff": inter // 4}, "shared": {"ff": inter // 2},
+           "router": {"experts": 16, "top": 2, "scale": 2.5, "groups": {"count": 4, "keep": 2}}}
+    delta = {"type": "delta", "mixer": {"heads": H, "kv_heads": G, "dim": FAMILY_HD, "vdim": FAMILY_HD, "conv": 4}, "mlp": mlp}
+    par = {"type": "parallel", "mlp": mlp,
+           "mixer": {"left": {"heads": H, "kv_heads": G, "dim": FAMILY_HD, "vdim": FAMILY_HD, "scale": FAMILY_HD ** -0.5,
+                              "rot": {"base": 10000.0, "dims": FAMILY_HD // 2}, "mask": {"size": 1024, "keep_first": 4}},
+                     "right": {"width": w, "blocks": w // 256, "conv": 4}, "left_scale": 1.0, "right_scale": 1.0}}
+    layers = [par if i % 4 == 3 else delta for i in range(FAMILY_LAYERS)]
+    kpz = parse_config_dict({"architecture": "Kipezen", "vocab": FAMILY_VOCAB, "width": w, "norm": {"eps": 1e-5}, "layers": layers})
+    return kpz, _family_configs(size)[0]
+
+
 def _weight_bytes(runner):
     seen, n = set(), 0
     import torch
@@ -420,8 +439,8 @@ def run_family(args):
     from inf_engine_b200 import Engine, StepEntry, SamplingConfig, kernels
     from inf_engine_b200.sampling import pack_rows, request_key
 
-    if args.family != "barerax":
-        print(f"--family {args.family}: unknown (known: barerax)")
+    if args.family not in ("barerax", "kipezen"):
+        print(f"--family {args.family}: unknown (known: barerax, kipezen)")
         return 2
     pk = peaks()
     torch.cuda.set_device(0)
@@ -623,7 +642,200 @@ def run_family(args):
                      "like_ms": rows[-2]["like_ms"], "like_frac_of_hbm": rows[-2]["like_frac_of_hbm"]})
         return rows
 
+    def kipezen_kernel_table(size):
+        """Every kernel that the Kipezen family added, alone, beside the like kernel of the closest family (Barerax, or
+        the Llama path where Barerax has none), at 2,048 tokens of one request and at 8 requests of one token."""
+        z = FAMILY_SIZES[size]
+        W, H, G, hd, inter = z["width"], z["heads"], z["kv"], FAMILY_HD, z["inter"]
+        N, B, dev, bf = PROMPT_LEN, 8, "cuda", torch.bfloat16
+        g = torch.Generator(device=dev).manual_seed(1)
+        rnd = lambda *shape: (torch.randn(*shape, device=dev, generator=g) * 0.5)
+        i32 = lambda v: torch.as_tensor(v, dtype=torch.int32, device=dev)
+        rows = []
+
+        def add(name, like, ms, ms_like, nbytes=None, nbytes_like=None, flops=None, flops_like=None, note=None):
+            rec = {"kernel": name, "like": like, "ms": ms, "like_ms": ms_like}
+            if nbytes is not None:
+                rec["frac_of_hbm"] = nbytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"]
+                if ms_like:
+                    rec["like_frac_of_hbm"] = (nbytes_like or nbytes) / (ms_like * 1e-3) / 1e9 / pk["hbm_gbs"]
+            if flops is not None:
+                rec["frac_of_bf16"] = flops / (ms * 1e-3) / 1e12 / pk["bf16_tflops"]
+                if ms_like:
+                    rec["like_frac_of_bf16"] = (flops_like or flops) / (ms_like * 1e-3) / 1e12 / pk["bf16_tflops"]
+            if note:
+                rec["note"] = note
+            rows.append(rec)
+
+        qs1, sl1 = i32([0, N]), i32([0])
+        qs8, sl8 = torch.arange(B + 1, dtype=torch.int32, device=dev), torch.arange(B, dtype=torch.int32, device=dev)
+        # the norm of a sublayer's output into the residual (and the next sublayer's input) | RMSNorm + residual sum
+        res, y, nxt = rnd(N, W), rnd(N, W).to(bf), torch.empty(N, W, device=dev, dtype=bf)
+        gain = (1 + 0.1 * rnd(W))
+        add("output norm into the residual (+ next input)", "rmsnorm(+residual sum)",
+            timed(lambda: kernels.outnorm_accumulate(res, y, gain, 1e-5, nxt)),
+            timed(lambda: kernels.rmsnorm(res, y, gain.to(bf), nxt, 1e-5)), N * W * (4 + 4 + 2 + 2))
+        # short convolution with state over q | k | v of a delta layer | SiLU(gate) * up (an elementwise pass)
+        C = 2 * G * hd + H * hd
+        xin, cw, cout = rnd(N, C + 2 * H + H * hd).to(bf), rnd(C, 4).to(bf), torch.empty(N, C, device=dev, dtype=bf)
+        cstate = torch.zeros(16, 3, C, device=dev, dtype=bf)
+        gu, h2 = rnd(N, 2 * inter).to(bf), torch.empty(N, inter, device=dev, dtype=bf)
+        add("short convolution + SiLU, prompt", "silu_mul",
+            timed(lambda: kernels.causal_conv(xin[:, :C], cw, None, cstate, cout, qs1, sl1, 1, activation="silu")),
+            timed(lambda: kernels.silu_mul(gu, h2, interleaved=True)), N * C * 4, N * inter * 6)
+        add("short convolution + SiLU, decode b8", None,
+            timed(lambda: kernels.causal_conv(xin[:B, :C], cw, None, cstate, cout[:B], qs8, sl8, B, activation="silu")), None,
+            B * C * (2 + 2 + 2 * 3 * 2))
+        # the gated delta rule | the generalized delta rule of Barerax
+        Wd = H * hd
+        q_, k_, v_ = cout[:, :G * hd], cout[:, G * hd:2 * G * hd], cout[:, 2 * G * hd:]
+        gate, b_pre, a_pre = xin[:, C:C + Wd], xin[:, C + Wd:C + Wd + H], xin[:, C + Wd + H:C + Wd + 2 * H]
+        a_log, dt_b, og = rnd(H).to(bf), rnd(H).to(bf), (1 + 0.1 * rnd(hd)).to(bf)
+        st = torch.zeros(16, H, hd, hd, device=dev)
+        mixed = torch.empty(N, Wd, device=dev, dtype=bf)
+        run_gd = lambda n, qs, sl, R: kernels.gated_delta(q_[:n], k_[:n], v_[:n], b_pre[:n], a_pre[:n], gate[:n], a_log, dt_b, og, st,
+                                                          mixed[:n], qs, sl, R, H, G, hd, hd, 1e-6, 1e-5)
+        proj, w_pre, vec = rnd(N, 5 * Wd + 64).to(bf), rnd(N, Wd), rnd(Wd).to(bf)
+        views = [proj[:, i * Wd:(i + 1) * Wd] for i in range(5)]
+        run_brx = lambda n, qs, sl, R: kernels.delta_rule(views[0][:n], views[1][:n], views[2][:n], views[4][:n], views[3][:n], w_pre[:n],
+                                                           vec, vec, vec, st, mixed[:n], qs, sl, R, H, hd, 0.6, 1e-6, 1e-5)
+        add("gated delta rule, prompt of 2,048 tokens (one request)", "generalized delta rule, prompt",
+            timed(lambda: run_gd(N, qs1, sl1, 1), reps=5), timed(lambda: run_brx(N, qs1, sl1, 1), reps=5),
+            N * (2 * G * hd + 3 * Wd) * 2 + 2 * H * hd * hd * 4, N * Wd * (5 * 2 + 4 + 2) + 2 * H * hd * hd * 4,
+            note="a token-by-token scan: the chain of %d dependent steps bounds it, not bytes" % N)
+        add("gated delta rule, decode b8", "generalized delta rule, decode",
+            timed(lambda: run_gd(B, qs8, sl8, B)), timed(lambda: run_brx(B, qs8, sl8, B)), B * 2 * H * hd * hd * 4)
+        # whole-row norm + pair rotation + cache write | head norm + cache write of Barerax
+        n_pages = B * N // PAGE
+        qkv = rnd(N, (H + 2 * G) * hd).to(bf)
+        q, kx, v = qkv[:, :H * hd], qkv[:, H * hd:(H + G) * hd], qkv[:, (H + G) * hd:]
+        kpool = torch.zeros(n_pages, G, PAGE, hd, device=dev, dtype=bf)
+        vpool = torch.zeros_like(kpool)
+        slot_map, pos = torch.arange(N, dtype=torch.int32, device=dev), torch.arange(N, dtype=torch.int32, device=dev)
+        qb, kb, vb, qg, kg = rnd(H * hd).to(bf), rnd(G * hd).to(bf), rnd(G * hd).to(bf), (1 + 0.1 * rnd(H * hd)).to(bf), (1 + 0.1 * rnd(G * hd)).to(bf)
+        inv_freq = (10000.0 ** (-2.0 * torch.arange(hd // 4, dtype=torch.float64) / (hd // 2))).to(dev)
+        hg = (1 + 0.1 * rnd(hd)).to(bf)
+        add("biases + whole-row norm + pair rotation + cache write", "q/k head norm + cache write",
+            timed(lambda: kernels.rownorm_rotate_write(q, kx, v, qb, kb, vb, qg, kg, 1e-5, inv_freq, hd // 2, pos, slot_map, kpool, vpool,
+                                                       H, G, hd, hd, PAGE)),
+            timed(lambda: kernels.headnorm_kv_write(q, kx, v, hg, hg, 1e-5, slot_map, kpool, vpool, H, G, hd, hd, PAGE)),
+            N * (H + 2 * G) * hd * 2 * 2)
+        # attention with a window and kept first keys | attention with a distance bias (Barerax)
+        from inf_engine_b200.parts.attention import PagedAttention
+        from inf_engine_b200.parts import CacheView, Runtime
+        from inf_engine_b200.engine.batch import KVGroupContext, StepContext
+        kpz, brx = _kipezen_configs(size)
+        rt = Runtime(dev, bf)
+
+        def attention_part(spec):
+            tensors = {n: ((1 + 0.1 * rnd(*e.shape)) if e.init == "gain" else rnd(*e.shape) * 0.1).to(bf)
+                       for n, e in PagedAttention.expected_tensors(spec).items()}
+            return PagedAttention(spec, tensors, rt)
+
+        def context(q_lens, before):
+            ctx = StepContext(rt, PAGE)
+            R, n = len(q_lens), sum(q_lens)
+            ctx.n_tokens, ctx.n_requests, ctx.n_logits = n, R, 0
+            starts = [0]
+            for ql in q_lens:
+                starts.append(starts[-1] + ql)
+            per = n_pages // R
+            ctx.q_start, ctx.ctx_before = i32(starts), i32(before)
+            ctx.positions = i32([b + t for ql, b in zip(q_lens, before) for t in range(ql)])
+            ctx.slots = i32(list(range(R)))
+            table_ = torch.arange(per * R, dtype=torch.int32, device=dev).view(R, per)
+            sm = i32([(r * per + (b + t) // PAGE) * PAGE + (b + t) % PAGE for r, (ql, b) in enumerate(zip(q_lens, before)) for t in range(ql)])
+            ctx.kv = [KVGroupContext(sm, table_)]
+            ctx.host = {"q_lens": list(q_lens), "ctx_before": list(before), "q_start": starts}
+            ctx.max_q_len, ctx.max_seq_len = max(q_lens), max(b + ql for ql, b in zip(q_lens, before))
+            ctx.keys_cap = ctx.max_seq_len
+            return ctx
+
+        att_k = attention_part(kpz.model_spec().layers[3].mixer.branches[0])
+        att_b = attention_part(brx.model_spec().layers[3].mixer)
+        view = CacheView("kv", 0, kpool, vpool, None, True)
+        window = 1024
+        pairs_b = N * (N + 1) // 2
+        pairs_k = pairs_b - (N - window) * (N - window + 1) // 2 + 4 * (N - window - 4)
+        ctx_p = context([N], [0])
+        qkv_p = rnd(N, (H + 2 * G) * hd).to(bf)
+        add("attention, prompt (window of 1,024 + 4 kept keys)", "attention, prompt (distance bias, every key)",
+            timed(lambda: att_k._rotate_write_attend(qkv_p.clone(), ctx_p, view), reps=5),
+            timed(lambda: att_b._rotate_write_attend(qkv_p.clone(), ctx_p, view), reps=5),
+            flops=4 * H * hd * pairs_k, flops_like=4 * H * hd * pairs_b)
+        ctx_d = context([1] * B, [N - 1] * B)
+        qkv_d = rnd(B, (H + 2 * G) * hd).to(bf)
+        add("attention, decode b8 x 2,048 keys (1,028 visible)", "attention, decode (distance bias, every key)",
+            timed(lambda: att_k._rotate_write_attend(qkv_d.clone(), ctx_d, view)),
+            timed(lambda: att_b._rotate_write_attend(qkv_d.clone(), ctx_d, view)),
+            B * (window + 4) * G * hd * 2 * 2, B * N * G * hd * 2 * 2)
+        # the recurrent block: block-diagonal gates (float32 products) and the scan
+        nb_ = W // 256
+        u, ypre = rnd(N, W).to(bf), rnd(N, W).to(bf)
+        ag, gates = rnd(nb_, 256, 256).to(bf), torch.empty(N, 2 * W, device=dev)
+        lam, rb = rnd(W).to(bf), rnd(W).to(bf)
+        sst, rout = torch.zeros(16, W, device=dev), torch.empty(N, W, device=dev, dtype=bf)
+        ms = timed(lambda: kernels.gemm_simt_batched(u, ag, gates[:, :W]))
+        rows.append({"kernel": "block-diagonal gate product, prompt (float32 on CUDA cores)", "like": None, "ms": ms,
+                     "tflops_f32": 2 * N * W * 256 / (ms * 1e-3) / 1e12})
+        add("linear recurrent unit scan, prompt of 2,048 tokens (one request)", "generalized delta rule, prompt",
+            timed(lambda: kernels.linear_recurrence(u, ypre, gates[:, :W], gates[:, W:], rb, rb, lam, sst, rout, qs1, sl1, 1, 8.0), reps=5),
+            rows[3]["like_ms"], N * W * (2 + 2 + 4 + 4 + 2), N * Wd * (5 * 2 + 4 + 2),
+            note="a scan over tokens, a channel a thread")
+        add("linear recurrent unit scan, decode b8", "generalized delta rule, decode",
+            timed(lambda: kernels.linear_recurrence(u[:B], ypre[:B], gates[:B, :W], gates[:B, W:], rb, rb, lam, sst, rout[:B], qs8, sl8, B, 8.0)),
+            rows[4]["like_ms"], B * W * (2 + 2 + 4 + 4 + 2 + 8), B * 2 * H * hd * hd * 4)
+        # the routed experts: route + sort, the two grouped products | the dense gate/up product of the Llama path
+        E, top, ffe = 16, 2, inter // 4
+        x = rnd(N, W).to(bf)
+        logits = rnd(N, E + 1) * 2
+        ids, wts, gt = torch.empty(N, top, dtype=torch.int32, device=dev), torch.empty(N, top, device=dev), torch.empty(N, device=dev)
+        sorted_pairs = torch.empty(N * top, dtype=torch.int32, device=dev)
+        tiles = torch.empty(kernels.moe_max_tiles(N * top, E), 4, dtype=torch.int32, device=dev)
+        def route_sort():
+            kernels.moe_route(logits, None, ids, wts, gt, E, top, 4, 2, 2.5, 1e-20, gate_col=E)
+            kernels.moe_sort(ids, E, sorted_pairs, tiles)
+        ms = timed(route_sort)
+        rows.append({"kernel": "route + sort, 2,048 tokens x 2 of 16 experts", "like": None, "ms": ms})
+        gate_up, down = (rnd(E, 2 * ffe, W) * 0.1).to(bf), (rnd(E, W, ffe) * 0.1).to(bf)
+        hid, yp = torch.empty(N * top, ffe, device=dev, dtype=bf), torch.empty(N * top, W, device=dev)
+        dense_w, dense_out = (rnd(2 * inter, W) * 0.1).to(bf), torch.empty(N, inter, device=dev, dtype=bf)
+        like_ms = timed(lambda: kernels.gemm_tcgen05(x, dense_w, dense_out, "silu_mul"))
+        add("experts' gate/up product with SiLU, prompt (2 of 16 experts a token)", "dense gate/up product with SiLU (tcgen05)",
+            timed(lambda: kernels.moe_gemm(x, gate_up, hid, sorted_pairs, tiles, top, gather=True, scatter=False, epi="silu_mul")),
+            like_ms, flops=2 * N * top * 2 * ffe * W, flops_like=2 * N * 2 * inter * W)
+        add("experts' down product, prompt", "dense gate/up product with SiLU (tcgen05)",
+            timed(lambda: kernels.moe_gemm(hid, down, yp, sorted_pairs, tiles, top, gather=False, scatter=True)),
+            like_ms, flops=2 * N * top * ffe * W, flops_like=2 * N * 2 * inter * W)
+        # decode: 8 tokens choose 2 of 16 experts; what must move is the chosen experts' weights
+        ids8 = ids[:B].contiguous()
+        sp8, tl8 = torch.empty(B * top, dtype=torch.int32, device=dev), torch.empty(kernels.moe_max_tiles(B * top, E), 4, dtype=torch.int32, device=dev)
+        kernels.moe_sort(ids8, E, sp8, tl8)
+        n_chosen = len(set(ids8.flatten().tolist()))
+        add("experts' gate/up product with SiLU, decode b8", "dense gate/up with SiLU, decode (streaming product)",
+            timed(lambda: kernels.moe_gemm(x[:B], gate_up, hid[:B * top], sp8, tl8, top, gather=True, scatter=False, epi="silu_mul")),
+            timed(lambda: kernels.gemm_stream(x[:B], dense_w, dense_out[:B], B, "silu_mul")),
+            n_chosen * 2 * ffe * W * 2, 2 * inter * W * 2)
+        return rows
+
     sizes = {}
+    if args.family == "kipezen":
+        for size in (args.family_sizes.split(",") if args.family_sizes else list(FAMILY_SIZES)):
+            kpz, brx = _kipezen_configs(size)
+            rec = {"kipezen": model_numbers_of(kpz, args.batch), "barerax": model_numbers_of(brx, args.batch)}
+            rec["kernels"] = kipezen_kernel_table(size)
+            sizes[size] = rec
+        clocks.stop()
+        print(json.dumps({"impl": "ours", "family": "kipezen", "dtype": "bf16", "n_gpus": 1, "steps": args.steps,
+                          "warmup": max(args.warmup, 3),
+                          "data": "synthetic: seeded random weights, uniform random prompt ids",
+                          "config": {"layers": FAMILY_LAYERS, "pattern": "delta, delta, delta, parallel", "vocab": FAMILY_VOCAB,
+                                     "head_dim": FAMILY_HD, "prompt": PROMPT_LEN, "decode_batch": args.batch, "page_size": PAGE,
+                                     "experts": "16, 2 a token from 2 of 4 groups, and a shared one",
+                                     "l2": "a 256 MB buffer is written before every timed kernel; model steps stream their weights",
+                                     "sizes": FAMILY_SIZES},
+                          "peaks": pk, "sizes": sizes, "clocks": clocks.summary(t_all0, time.perf_counter())}))
+        return 0
     for size in (args.family_sizes.split(",") if args.family_sizes else list(FAMILY_SIZES)):
         brx, llama = _family_configs(size)
         rec = {"barerax": model_numbers_of(brx, args.batch), "llama": model_numbers_of(llama, args.batch)}
@@ -825,7 +1037,7 @@ def main():
     ap.add_argument("--no-workloads", action="store_true",
                     help="leave out the two continuous-batching workloads at the other models' sizes")
     ap.add_argument("--family", default=None, metavar="NAME",
-                    help="instead of the default workload: prefill and decode of another model family (barerax) at sizes like "
+                    help="instead of the default workload: prefill and decode of another model family (barerax, kipezen) at sizes like "
                          "a real model's layers, beside a Llama model of equal size, and its kernels beside the like ones")
     ap.add_argument("--family-sizes", default=None, help="comma-separated subset of the family's sizes (w1024,w2048)")
     ap.add_argument("--workload", default=None, metavar="N:MIN:MAX:NEW[:TEMP]",

@@ -44,7 +44,6 @@ __global__ void __launch_bounds__(GS_THREADS) gemm_simt_kernel(const TA* __restr
       Ws[lc + u][lr] = (wn < N && k < K) ? to_f32(W[(size_t)wn * ldw + k]) : 0.f;
     }
     __syncthreads();
-#ifdef IE_SIMT_CHAIN
 #pragma unroll
     for (int kk = 0; kk < GS_BK; ++kk) {
       float a[4], b[4];
@@ -57,31 +56,6 @@ __global__ void __launch_bounds__(GS_THREADS) gemm_simt_kernel(const TA* __restr
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
     }
-#else
-    // the slab's 16 products are summed by themselves and then added to the total: the rounding of a long sum
-    // grows with K / 16 + 16 steps instead of K
-    float part[4][4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-      for (int j = 0; j < 4; ++j) part[i][j] = 0.f;
-#pragma unroll
-    for (int kk = 0; kk < GS_BK; ++kk) {
-      float a[4], b[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) b[j] = Ws[kk][tx * 4 + j];
-#pragma unroll
-      for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) part[i][j] = fmaf(a[i], b[j], part[i][j]);
-    }
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-      for (int j = 0; j < 4; ++j) acc[i][j] += part[i][j];
-#endif
     __syncthreads();
   }
 #pragma unroll

@@ -3,9 +3,10 @@
 //            groups of neighbouring experts kept, the top experts among them, their normalised weights, and the
 //            shared expert's gate;
 //   sort     the (token, choice) pairs ordered by expert, and a table of row tiles, none of which spans two experts;
-//   product  C[pair] = A[token of pair] W[expert of pair]^T over those tiles on CUDA cores (float32 products and
-//            sums, every output one accumulator that walks k upward, so a row's result does not depend on which
-//            tile or step it is in), optionally with silu(gate) * up in the epilogue;
+//   product  C[pair] = A[token of pair] W[expert of pair]^T over those tiles, optionally with silu(gate) * up in the
+//            epilogue: on CUDA cores (float32 products and sums, every output one accumulator that walks k upward) for
+//            the 32-bit path, on tensor cores (mma.sync, float32 accumulators) for bfloat16 operands; either way a
+//            row's result does not depend on which tile or step it is in;
 //   combine  out[token] = sum over its choices of weight * y[pair] + gate * shared[token], choices in order.
 #include "common.cuh"
 
@@ -220,7 +221,6 @@ moe_gemm_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TC* __restri
       Ws[lc + u][lr] = (wn < N && k < K) ? to_f32(Wexp[(size_t)wn * K + k]) : 0.f;
     }
     __syncthreads();
-#ifdef IE_SIMT_CHAIN
 #pragma unroll
     for (int kk = 0; kk < MG_BK; ++kk) {
       float a[4], b[4];
@@ -233,31 +233,6 @@ moe_gemm_kernel(const TA* __restrict__ A, const TW* __restrict__ W, TC* __restri
 #pragma unroll
         for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
     }
-#else
-    // the slab's 16 products are summed by themselves and then added to the total: the rounding of a long sum
-    // grows with K / 16 + 16 steps instead of K
-    float part[4][4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-      for (int j = 0; j < 4; ++j) part[i][j] = 0.f;
-#pragma unroll
-    for (int kk = 0; kk < MG_BK; ++kk) {
-      float a[4], b[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) b[j] = Ws[kk][tx * 4 + j];
-#pragma unroll
-      for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) part[i][j] = fmaf(a[i], b[j], part[i][j]);
-    }
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-      for (int j = 0; j < 4; ++j) acc[i][j] += part[i][j];
-#endif
     __syncthreads();
   }
 #pragma unroll
@@ -292,6 +267,129 @@ static int launch_moe_gemm(const void* A, const void* W, void* C, const int* sor
                   tiles, N, K, lda, ldc, wes, top, gather, scatter, epi);
 }
 
+// ---- the same product on tensor cores, for bfloat16 operands (mma.sync m16n8k16, float32 accumulators): a block
+// takes a tile of 64 pairs by 128 outputs and walks K in slabs of 32 through two shared-memory stages filled with
+// 16-byte cp.async copies (a gathered row of A is one such stream); eight warps, two along the rows and four along
+// the outputs, 32 x 32 each.  A row's sum walks k upward in the tensor core's own fixed order whatever tile the row
+// lies in, so a pair's result still does not depend on its place or on the rest of the step.  K and the row strides
+// must be multiples of 8 elements (16-byte copies); other shapes take the CUDA-core kernel above.
+#define MM_BM 64
+#define MM_BN 128
+#define MM_BK 32
+#define MM_LD 40          // row stride in shared memory, bfloat16 elements: 80 bytes keep ldmatrix's 8 rows on 8 bank groups
+#define MM_THREADS 256
+
+__device__ __forceinline__ uint32_t mm_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mm_cp16(uint32_t dst, const void* src, int bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mm_ldsm4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mm_mma(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <typename TC>
+__global__ void __launch_bounds__(MM_THREADS)
+moe_gemm_mma_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, TC* __restrict__ C,
+                    const int* __restrict__ sorted, const int* __restrict__ tiles, int N, int K, int lda, int ldc,
+                    long long w_expert_stride, int top, int gather, int scatter, int epi) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ __align__(16) bf16 As[2][MM_BM * MM_LD];
+  __shared__ __align__(16) bf16 Ws[2][MM_BN * MM_LD];
+  __shared__ int a_row[MM_BM], c_row[MM_BM];
+  const int tile = blockIdx.y;
+  const int rows = tiles[4 * tile + 2];
+  if (rows <= 0) return;
+  const int expert = tiles[4 * tile], pos0 = tiles[4 * tile + 1];
+  const int n0 = blockIdx.x * MM_BN;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid < MM_BM) {
+    int ar = -1, cr = -1;
+    if (tid < rows) {
+      const int pair = sorted[pos0 + tid];
+      ar = gather ? pair / top : pos0 + tid;
+      cr = scatter ? pair : pos0 + tid;
+    }
+    a_row[tid] = ar;
+    c_row[tid] = cr;
+  }
+  __syncthreads();
+  const bf16* Wexp = W + (size_t)expert * w_expert_stride;
+  const int lrow = tid >> 2, lch = (tid & 3) * 8;          // this thread's row and 8-element chunk of a slab
+  const int my_a = a_row[lrow];
+  auto load_stage = [&](int s, int k0) {
+    const int k = k0 + lch;
+    const bool kin = k < K;
+    mm_cp16(mm_smem(&As[s][lrow * MM_LD + lch]), (my_a >= 0 && kin) ? (const void*)(A + (size_t)my_a * lda + k) : (const void*)A,
+            (my_a >= 0 && kin) ? 16 : 0);
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int wr = lrow + 64 * u, wn = n0 + wr;
+      mm_cp16(mm_smem(&Ws[s][wr * MM_LD + lch]), (wn < N && kin) ? (const void*)(Wexp + (size_t)wn * K + k) : (const void*)W,
+              (wn < N && kin) ? 16 : 0);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  const int wm = warp & 1, wn = warp >> 1;                   // 2 x 4 warps, 32 x 32 outputs each
+  float acc[2][4][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j][0] = acc[i][j][1] = acc[i][j][2] = acc[i][j][3] = 0.f;
+  const int nk = (K + MM_BK - 1) / MM_BK;
+  load_stage(0, 0);
+  for (int kt = 0; kt < nk; ++kt) {
+    const int s = kt & 1;
+    if (kt + 1 < nk) {
+      load_stage(s ^ 1, (kt + 1) * MM_BK);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+#pragma unroll
+    for (int ks = 0; ks < MM_BK; ks += 16) {
+      uint32_t af[2][4], bfr[2][4];
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
+        mm_ldsm4(af[mt], mm_smem(&As[s][(wm * 32 + mt * 16 + (lane & 15)) * MM_LD + ks + (lane >> 4) * 8]));
+#pragma unroll
+      for (int np = 0; np < 2; ++np)
+        mm_ldsm4(bfr[np], mm_smem(&Ws[s][(wn * 32 + np * 16 + (lane & 7) + (lane >> 4) * 8) * MM_LD + ks + ((lane >> 3) & 1) * 8]));
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) mm_mma(acc[mt][nt], af[mt], bfr[nt >> 1][(nt & 1) * 2], bfr[nt >> 1][(nt & 1) * 2 + 1]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt) {
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int cr = c_row[wm * 32 + mt * 16 + (lane >> 2) + half * 8];
+      if (cr < 0) continue;
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+        const int n = n0 + wn * 32 + nt * 8 + (lane & 3) * 2;
+        const float x0 = acc[mt][nt][half * 2], x1 = acc[mt][nt][half * 2 + 1];
+        if (epi == 1) {
+          if (n + 1 < N) C[(size_t)cr * ldc + (n >> 1)] = from_f32<TC>(x0 / (1.f + expf(-x0)) * x1);
+        } else {
+          if (n < N) C[(size_t)cr * ldc + n] = from_f32<TC>(x0);
+          if (n + 1 < N) C[(size_t)cr * ldc + n + 1] = from_f32<TC>(x1);
+        }
+      }
+    }
+  }
+}
+
 extern "C" int ie_moe_tile_rows() { return MG_BM; }
 
 extern "C" int ie_moe_gemm(const void* A, int a_dtype, const void* W, int w_dtype, void* C, int c_dtype,
@@ -299,6 +397,16 @@ extern "C" int ie_moe_gemm(const void* A, int a_dtype, const void* W, int w_dtyp
                            long long w_expert_stride, int top, int gather, int scatter, int epi, cudaStream_t stream) {
   if (max_tiles <= 0 || N <= 0) return IE_OK;
   if (K <= 0 || top <= 0 || (epi == 1 && (N & 1))) return IE_BAD_SIZE;
+  if (a_dtype == IE_BF16 && w_dtype == IE_BF16 && K % 8 == 0 && lda % 8 == 0 && w_expert_stride % 8 == 0 &&
+      (((uintptr_t)A | (uintptr_t)W) & 15) == 0) {
+    static_assert(MM_BM == MG_BM, "both kernels walk the same tiles");
+    dim3 grid((N + MM_BN - 1) / MM_BN, max_tiles);
+    if (c_dtype == IE_BF16)
+      return launch_k(moe_gemm_mma_kernel<bf16>, grid, MM_THREADS, 0, stream, (const bf16*)A, (const bf16*)W, (bf16*)C,
+                      sorted, tiles, N, K, lda, ldc, w_expert_stride, top, gather, scatter, epi);
+    return launch_k(moe_gemm_mma_kernel<float>, grid, MM_THREADS, 0, stream, (const bf16*)A, (const bf16*)W, (float*)C,
+                    sorted, tiles, N, K, lda, ldc, w_expert_stride, top, gather, scatter, epi);
+  }
   const int code = a_dtype * 4 + w_dtype * 2 + c_dtype;
 #define MG_GO(TA, TW, TC)                                                                                         \
   return launch_moe_gemm<TA, TW, TC>(A, W, C, sorted, tiles, max_tiles, N, K, lda, ldc, w_expert_stride, top, gather, \
