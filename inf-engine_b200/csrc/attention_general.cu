@@ -247,4 +247,152 @@ extern "C" int ie_attention_general(const void* q, void* out, const void* kpool,
   return IE_BAD_DTYPE;
 }
 
+// ------------------------------------------------------------------ few rows a request (decode steps)
+// The tile kernel above gives a (request, kv head) one block, which for a request that brings a single token walks
+// all its keys alone.  This one gives every (token, query head) of a request that brings at most `max_rows` (token,
+// head-in-group) rows a block of eight warps: warp w takes the visible keys w, w + 8, ... (the kept first keys, then
+// the window's), a key at a time with the head's dimensions spread over the lanes, four keys' loads in flight; each
+// warp keeps its own running maximum, sum and output, and the eight are merged in shared memory in warp order.  Same
+// arithmetic as above (float32 scores, weights and sums), same options.  Requests with more rows are left to the tile
+// kernel, whose work list then names only those.
+#define AR_WARPS 8
+#define AR_MAX_PER_LANE 8   // head sizes up to 256
+
+template <typename T>
+__global__ void __launch_bounds__(AR_WARPS * 32) attention_rows_kernel(AttnGeneralParams p, int n_requests, int max_rows) {
+  __shared__ float s_m[AR_WARPS], s_l[AR_WARPS];
+  extern __shared__ float s_acc[];                 // [AR_WARPS][hd_v]
+  pdl_trigger();
+  pdl_wait();
+  const int n = blockIdx.x, head = blockIdx.y;
+  int lo = 0, hi = n_requests;                     // the request r with q_start[r] <= n < q_start[r + 1]
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (p.q_start[mid] <= n) lo = mid; else hi = mid;
+  }
+  const int r_id = lo;
+  const int group = p.n_heads / p.n_kv_heads;
+  const int q0 = p.q_start[r_id], q_len = p.q_start[r_id + 1] - q0;
+  if (q_len * group > max_rows) return;            // the tile kernel's
+  const int hd = p.hd, hdv = p.hd_v;
+  const int c = head / group;
+  const int limit = p.ctx_before[r_id] + (n - q0);                       // last visible key
+  const int first = p.window > 0 ? max(0, limit - p.window + 1) : 0;
+  const int n_keep = p.window > 0 ? min(p.keep_first, first) : 0;         // kept keys that the window does not hold anyway
+  const int n_vis = n_keep + (limit - first + 1);
+  const int* table = p.block_table + (size_t)r_id * p.table_stride;
+  const T* kpool = (const T*)p.kpool;
+  const T* vpool = (const T*)p.vpool;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const T* qrow = (const T*)p.q + (size_t)n * p.q_stride + head * hd;
+  float qv[AR_MAX_PER_LANE], acc[AR_MAX_PER_LANE];
+#pragma unroll
+  for (int j = 0; j < AR_MAX_PER_LANE; ++j) {
+    const int d = lane + 32 * j;
+    qv[j] = d < hd ? to_f32(qrow[d]) : 0.f;
+    acc[j] = 0.f;
+  }
+  const float my_scale = p.head_scale != nullptr ? p.scale * p.head_scale[head] : p.scale;
+  const float* my_bias = p.score_bias != nullptr ? p.score_bias + (size_t)head * p.bias_dists : nullptr;
+  float m_run = -INFINITY, l_run = 0.f;
+  for (int i0 = warp; i0 < n_vis; i0 += 4 * AR_WARPS) {
+    float part[4], vv[4][AR_MAX_PER_LANE];          // the values are fetched with the keys: one memory latency a round
+    int kpos[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int idx = i0 + u * AR_WARPS;
+      part[u] = 0.f;
+      kpos[u] = -1;
+      if (idx < n_vis) {
+        const int kp = idx < n_keep ? idx : first + (idx - n_keep);
+        const int page = IE_PAGE(table[kp / p.page_size]);
+        if (page >= 0) {
+          kpos[u] = kp;
+          const size_t at = ((size_t)page * p.n_kv_heads + c) * p.page_size + (kp % p.page_size);
+          const T* krow = kpool + at * hd;
+          const T* vrow = vpool + at * hdv;
+          T kraw[AR_MAX_PER_LANE], vraw[AR_MAX_PER_LANE];
+#pragma unroll
+          for (int j = 0; j < AR_MAX_PER_LANE; ++j) {
+            const int d = lane + 32 * j;
+            if (d < hd) kraw[j] = krow[d];
+            if (d < hdv) vraw[j] = vrow[d];
+          }
+#pragma unroll
+          for (int j = 0; j < AR_MAX_PER_LANE; ++j) {
+            const int d = lane + 32 * j;
+            if (d < hd) part[u] = fmaf(qv[j], to_f32(kraw[j]), part[u]);
+            vv[u][j] = d < hdv ? to_f32(vraw[j]) : 0.f;
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (kpos[u] < 0) continue;                   // (the same in every lane of the warp)
+      float sc = warp_sum(part[u]) * my_scale;
+      if (my_bias != nullptr) sc += my_bias[min(limit - kpos[u], p.bias_dists - 1)];
+      const float m_new = fmaxf(m_run, sc);
+      const float alpha = expf(m_run - m_new), e = expf(sc - m_new);
+      l_run = l_run * alpha + e;
+      m_run = m_new;
+#pragma unroll
+      for (int j = 0; j < AR_MAX_PER_LANE; ++j) {
+        const int d = lane + 32 * j;
+        if (d < hdv) acc[j] = fmaf(e, vv[u][j], acc[j] * alpha);
+      }
+    }
+  }
+  if (lane == 0) {
+    s_m[warp] = m_run;
+    s_l[warp] = l_run;
+  }
+#pragma unroll
+  for (int j = 0; j < AR_MAX_PER_LANE; ++j) {
+    const int d = lane + 32 * j;
+    if (d < hdv) s_acc[warp * hdv + d] = acc[j];
+  }
+  __syncthreads();
+  float m_all = -INFINITY;
+#pragma unroll
+  for (int w = 0; w < AR_WARPS; ++w) m_all = fmaxf(m_all, s_m[w]);
+  float l_all = 0.f;
+#pragma unroll
+  for (int w = 0; w < AR_WARPS; ++w) l_all += s_m[w] == -INFINITY ? 0.f : s_l[w] * expf(s_m[w] - m_all);
+  const float inv = l_all > 0.f ? p.out_scale / l_all : 0.f;
+  T* o = (T*)p.out + (size_t)n * p.out_stride + head * hdv;
+  for (int d = threadIdx.x; d < hdv; d += AR_WARPS * 32) {
+    float total = 0.f;
+#pragma unroll
+    for (int w = 0; w < AR_WARPS; ++w)
+      if (s_m[w] != -INFINITY) total = fmaf(s_acc[w * hdv + d], expf(s_m[w] - m_all), total);
+    o[d] = from_f32<T>(total * inv);
+  }
+}
+
+extern "C" int ie_attention_rows(const void* q, void* out, const void* kpool, const void* vpool, const int* block_table,
+                                 const int* q_start, const int* ctx_before, int q_stride, int out_stride, int table_stride,
+                                 int n_tokens, int n_requests, int max_rows, int n_heads, int n_kv_heads, int hd,
+                                 int page_size, int window, float scale, int act_dtype, const float* score_bias,
+                                 int bias_dists, const float* head_scale, int hd_v, int keep_first, float out_scale,
+                                 cudaStream_t stream) {
+  if (n_tokens <= 0 || n_requests <= 0) return IE_OK;
+  if (hd_v <= 0) hd_v = hd;
+  if (hd <= 0 || hd > 32 * AR_MAX_PER_LANE || hd_v > 32 * AR_MAX_PER_LANE) return IE_BAD_SIZE;
+  if (n_kv_heads <= 0 || n_heads % n_kv_heads || n_heads > 65535) return IE_BAD_SIZE;
+  if (score_bias != nullptr && bias_dists <= 0) return IE_BAD_SIZE;
+  AttnGeneralParams p;
+  p.q = q; p.out = out; p.kpool = kpool; p.vpool = vpool; p.block_table = block_table;
+  p.q_start = q_start; p.ctx_before = ctx_before; p.work_req = nullptr; p.work_pair0 = nullptr;
+  p.q_stride = q_stride; p.out_stride = out_stride; p.table_stride = table_stride;
+  p.n_work = 0; p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.hd = hd; p.page_size = page_size;
+  p.window = window; p.scale = scale; p.score_bias = score_bias; p.bias_dists = bias_dists;
+  p.head_scale = head_scale; p.hd_v = hd_v; p.keep_first = keep_first > 0 ? keep_first : 0; p.out_scale = out_scale;
+  const size_t smem = sizeof(float) * AR_WARPS * (size_t)hd_v;
+  dim3 grid(n_tokens, n_heads);
+  if (act_dtype == IE_F32) return launch_k(attention_rows_kernel<float>, grid, AR_WARPS * 32, smem, stream, p, n_requests, max_rows);
+  if (act_dtype == IE_BF16) return launch_k(attention_rows_kernel<bf16>, grid, AR_WARPS * 32, smem, stream, p, n_requests, max_rows);
+  return IE_BAD_DTYPE;
+}
+
 IE_CHECK_API(attention_general)

@@ -86,6 +86,10 @@ struct MmaAttnParams {
   const float* score_bias;
   int bias_dists;
   const float* head_scale;
+  // prompt kernel: beside a window the first keep_first keys of a sequence stay visible to every later query;
+  // out_scale multiplies the output
+  int keep_first;
+  float out_scale;
 };
 
 __device__ __forceinline__ RowScore row_score(const MmaAttnParams& p, int head0, int head1) {
@@ -218,7 +222,7 @@ template <int KT, bool HALF = false>
 __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[KSTEPS][4], float (&o)[NT_O][4], float (&m)[2],
                                           float (&l)[2], uint32_t ks_addr, uint32_t vs_addr, int k0, int lim0,
                                           int lim1, int first0, int first1, bool need_mask, float scale_log2,
-                                          int lane, const RowScore& rs) {
+                                          int lane, const RowScore& rs, int keep = 0) {
   constexpr int NT_S = KT / 8;
   float s[NT_S][4];
 #pragma unroll
@@ -264,11 +268,12 @@ __device__ __forceinline__ void warp_tile(const uint32_t (&qf)[KSTEPS][4], float
   for (int i = 0; i < NT_S; ++i) {
     if (need_mask) {
       const int kp = k0 + i * 8 + col;
-      if (kp > lim0 || kp < first0) s[i][0] = -INFINITY;
-      if (kp + 1 > lim0 || kp + 1 < first0) s[i][1] = -INFINITY;
+      // (keep: keys below it stay visible whatever the window says)
+      if (kp > lim0 || (kp < first0 && kp >= keep)) s[i][0] = -INFINITY;
+      if (kp + 1 > lim0 || (kp + 1 < first0 && kp + 1 >= keep)) s[i][1] = -INFINITY;
       if (!HALF) {
-        if (kp > lim1 || kp < first1) s[i][2] = -INFINITY;
-        if (kp + 1 > lim1 || kp + 1 < first1) s[i][3] = -INFINITY;
+        if (kp > lim1 || (kp < first1 && kp >= keep)) s[i][2] = -INFINITY;
+        if (kp + 1 > lim1 || (kp + 1 < first1 && kp + 1 >= keep)) s[i][3] = -INFINITY;
       }
     }
     mx0 = fmaxf(mx0, fmaxf(s[i][0], s[i][1]));
@@ -412,14 +417,23 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(MmaAtt
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
   const uint32_t base = smem_u32(smem);
-  const int n_tiles = (k_end - k_begin + PF_KT - 1) / PF_KT;
-  load_kv_tile<PF_KT, PF_THREADS>(p, table, c, k_begin, k_end, base, base + PF_KT * HD * 2, tid);
+  // kept first keys: their tiles come first, then the walk jumps to the window's first tile (when the window
+  // reaches down to them anyway the walk simply starts at key 0)
+  const int keep = p.window > 0 ? p.keep_first : 0;
+  int n_keep_tiles = (keep + PF_KT - 1) / PF_KT;
+  if (n_keep_tiles * PF_KT >= k_begin) {
+    k_begin = keep > 0 ? 0 : k_begin;
+    n_keep_tiles = 0;
+  }
+  const int n_tiles = n_keep_tiles + (k_end - k_begin + PF_KT - 1) / PF_KT;
+  auto tile_key = [&](int i) { return i < n_keep_tiles ? i * PF_KT : k_begin + (i - n_keep_tiles) * PF_KT; };
+  load_kv_tile<PF_KT, PF_THREADS>(p, table, c, tile_key(0), k_end, base, base + PF_KT * HD * 2, tid);
   cp_async_commit();
   for (int i = 0; i < n_tiles; ++i) {
-    const int k0 = k_begin + i * PF_KT;
+    const int k0 = tile_key(i);
     if (i + 1 < n_tiles) {
       const uint32_t nb = base + ((i + 1) & 1) * PF_STAGE_BYTES;
-      load_kv_tile<PF_KT, PF_THREADS>(p, table, c, k0 + PF_KT, k_end, nb, nb + PF_KT * HD * 2, tid);
+      load_kv_tile<PF_KT, PF_THREADS>(p, table, c, tile_key(i + 1), k_end, nb, nb + PF_KT * HD * 2, tid);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -427,11 +441,11 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(MmaAtt
     }
     __syncthreads();
     // skip tiles that no row of this warp can see
-    if (warp_has_rows && k0 <= w_max_lim && k0 + PF_KT > w_min_first) {
+    if (warp_has_rows && k0 <= w_max_lim && (k0 + PF_KT > w_min_first || k0 < keep)) {
       const uint32_t sb = base + (i & 1) * PF_STAGE_BYTES;
       const bool need_mask = (k0 + PF_KT - 1 > w_min_lim) || (k0 < w_max_first);
       warp_tile<PF_KT>(qf, o, m, l, sb, sb + PF_KT * HD * 2, k0, lim0, lim1, first0, first1, need_mask,
-                       p.scale_log2, lane, rs);
+                       p.scale_log2, lane, rs, keep);
     }
     __syncthreads();
   }
@@ -443,14 +457,14 @@ __global__ void __launch_bounds__(PF_WARPS * 32) attention_prefill_kernel(MmaAtt
   l[1] += __shfl_xor_sync(0xffffffffu, l[1], 2);
   const int col = (lane & 3) * 2;
   if (v0) {
-    const float inv = l[0] > 0.f ? 1.f / l[0] : 0.f;
+    const float inv = l[0] > 0.f ? p.out_scale / l[0] : 0.f;
     bf16* dst = p.out + (size_t)(q0 + t0) * p.out_stride + (c * group + (pr0 - t0 * group)) * HD;
 #pragma unroll
     for (int i = 0; i < NT_O; ++i)
       *reinterpret_cast<uint32_t*>(dst + i * 8 + col) = pack_bf16(o[i][0] * inv, o[i][1] * inv);
   }
   if (v1) {
-    const float inv = l[1] > 0.f ? 1.f / l[1] : 0.f;
+    const float inv = l[1] > 0.f ? p.out_scale / l[1] : 0.f;
     bf16* dst = p.out + (size_t)(q0 + t1) * p.out_stride + (c * group + (pr1 - t1 * group)) * HD;
 #pragma unroll
     for (int i = 0; i < NT_O; ++i)
@@ -922,6 +936,7 @@ static void fill(MmaAttnParams& p, const void* q, void* out, const void* kpool, 
   p.fuse = 0; p.k_new = nullptr; p.v_new = nullptr; p.kv_stride = 0; p.cos_t = nullptr; p.sin_t = nullptr;
   p.positions = nullptr; p.slot_mapping = nullptr;
   p.score_bias = nullptr; p.bias_dists = 0; p.head_scale = nullptr;
+  p.keep_first = 0; p.out_scale = 1.f;
   p.page_shift = -1;
   if ((page_size & (page_size - 1)) == 0)
     for (int b = 0; b < 31; ++b)
@@ -953,7 +968,8 @@ static int prefill_launch(const void* q, void* out, const void* kpool, const voi
                                     const int* work_req, const int* work_pair0, int q_stride, int out_stride,
                                     int table_stride, int n_work, int n_heads, int n_kv_heads, int hd, int page_size,
                                     int window, float scale, int rows, const float* score_bias, int bias_dists,
-                                    const float* head_scale, cudaStream_t stream) {
+                                    const float* head_scale, cudaStream_t stream, int keep_first = 0,
+                                    float out_scale = 1.f) {
   if (rows != 64 && rows != 128) return IE_BAD_SIZE;
   if (n_work <= 0) return IE_OK;
   int rc = check_common(q, out, kpool, vpool, q_stride, out_stride, n_heads, n_kv_heads, hd, page_size);
@@ -964,6 +980,7 @@ static int prefill_launch(const void* q, void* out, const void* kpool, const voi
   fill(p, q, out, kpool, vpool, block_table, q_start, ctx_before, q_stride, out_stride, table_stride, n_heads,
        n_kv_heads, page_size, window, scale);
   p.score_bias = score_bias; p.bias_dists = bias_dists; p.head_scale = head_scale;
+  p.keep_first = keep_first > 0 ? keep_first : 0; p.out_scale = out_scale;
   p.work_req = work_req;
   p.work_pair0 = work_pair0;
   const int smem = 2 * PF_STAGE_BYTES;
@@ -998,6 +1015,20 @@ extern "C" int ie_attention_prefill_biased(const void* q, void* out, const void*
   return prefill_launch(q, out, kpool, vpool, block_table, q_start, ctx_before, work_req, work_pair0, q_stride,
                         out_stride, table_stride, n_work, n_heads, n_kv_heads, hd, page_size, window, scale, rows,
                         score_bias, bias_dists, head_scale, stream);
+}
+
+// the bias build's prompt kernel with kept first keys beside the window and a multiplier of the output
+extern "C" int ie_attention_prefill_kept(const void* q, void* out, const void* kpool, const void* vpool,
+                                         const int* block_table, const int* q_start, const int* ctx_before,
+                                         const int* work_req, const int* work_pair0, int q_stride, int out_stride,
+                                         int table_stride, int n_work, int n_heads, int n_kv_heads, int hd,
+                                         int page_size, int window, float scale, int rows, const float* score_bias,
+                                         int bias_dists, const float* head_scale, int keep_first, float out_scale,
+                                         cudaStream_t stream) {
+  if (!BIASED) return IE_BAD_SIZE;
+  return prefill_launch(q, out, kpool, vpool, block_table, q_start, ctx_before, work_req, work_pair0, q_stride,
+                        out_stride, table_stride, n_work, n_heads, n_kv_heads, hd, page_size, window, scale, rows,
+                        score_bias, bias_dists, head_scale, stream, keep_first, out_scale);
 }
 
 // Scratch needed by the decode kernel, in 4-byte words: IE_DECODE_TICKET_WORDS tickets (one per

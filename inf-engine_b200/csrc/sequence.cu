@@ -95,11 +95,13 @@ extern "C" int ie_outnorm_accumulate(float* residual, const void* y, int y_dtype
 // out[t, c] = act(bias[c] + sum_j w[c, j] * x[t - (taps - 1 - j), c]): the last column of w multiplies the current
 // token's input.  Inputs before the first token of the step come from the request's state, [taps - 1, channels] in
 // the activation type (the last inputs of the sequence so far, oldest first; zero when the sequence starts), and the
-// state is then moved on by the step's tokens.  A block owns 32 channels of one request: its 8 rows of threads take
-// the request's tokens in turn, and when all have read what they need of the old state, one row writes the new
-// one.  So any cut of a sequence into steps gives the same outputs.
+// state is then moved on by the step's tokens.  A block owns 32 channels of one chunk of 64 tokens of one request: its
+// 8 rows of threads take the chunk's tokens in turn.  Only a request's first chunk reads the old state, and that
+// block, when all its rows have read what they need of it, writes the new one (from the request's last tokens of the
+// step, which no kernel writes meanwhile).  So any cut of a sequence into steps gives the same outputs.
 #define CONV_CH 32
 #define CONV_TL 8
+#define CONV_CHUNK 64
 #define CONV_MAX_TAPS 16
 
 template <typename TA, typename TW>
@@ -114,6 +116,8 @@ causal_conv_kernel(const TA* __restrict__ x, int x_stride, const TW* __restrict_
   const int tl = threadIdx.y;
   const int req = blockIdx.y;
   const int q0 = q_start[req], q1 = q_start[req + 1];
+  const int t_lo = q0 + blockIdx.z * CONV_CHUNK, t_hi = min(q1, t_lo + CONV_CHUNK);
+  if (t_lo >= q1 && blockIdx.z > 0) return;                  // a shorter request than the step's longest
   const int slot = IE_SLOT(slots[req]);
   const bool live = c < channels;
   TA* st = (slot >= 0 && live) ? state + (size_t)slot * state_slot_stride + c : nullptr;   // element i at st[i * channels]
@@ -122,7 +126,7 @@ causal_conv_kernel(const TA* __restrict__ x, int x_stride, const TW* __restrict_
   for (int j = 0; j < CONV_MAX_TAPS; ++j) wv[j] = (live && j < taps) ? to_f32(w[(size_t)c * taps + j]) : 0.f;
   const float b = (live && bias != nullptr) ? to_f32(bias[c]) : 0.f;
   if (live) {
-    for (int t = q0 + tl; t < q1; t += CONV_TL) {
+    for (int t = t_lo + tl; t < t_hi; t += CONV_TL) {
       float acc = b;
 #pragma unroll
       for (int j = 0; j < CONV_MAX_TAPS; ++j) {
@@ -138,6 +142,7 @@ causal_conv_kernel(const TA* __restrict__ x, int x_stride, const TW* __restrict_
       out[(size_t)t * out_stride + c] = from_f32<TA>(acc);
     }
   }
+  if (blockIdx.z > 0) return;
   __syncthreads();
   if (write_state && st != nullptr && tl == 0) {
     const int n = q1 - q0, keep = taps - 1;
@@ -159,10 +164,12 @@ causal_conv_kernel(const TA* __restrict__ x, int x_stride, const TW* __restrict_
 extern "C" int ie_causal_conv(const void* x, int x_stride, const void* w, const void* bias, int w_dtype, void* state,
                               long long state_slot_stride, void* out, int out_stride, const int* q_start,
                               const int* slots, int n_requests, int channels, int taps, int activation,
-                              int write_state, int act_dtype, cudaStream_t stream) {
+                              int write_state, int act_dtype, int max_q_len, cudaStream_t stream) {
   if (n_requests <= 0 || channels <= 0) return IE_OK;
-  if (taps < 1 || taps > CONV_MAX_TAPS) return IE_BAD_SIZE;
-  dim3 grid((channels + CONV_CH - 1) / CONV_CH, n_requests), block(CONV_CH, CONV_TL);
+  if (taps < 1 || taps > CONV_MAX_TAPS || max_q_len < 1) return IE_BAD_SIZE;
+  const int chunks = (max_q_len + CONV_CHUNK - 1) / CONV_CHUNK;       // of the step's longest request
+  if (chunks > 65535) return IE_BAD_SIZE;
+  dim3 grid((channels + CONV_CH - 1) / CONV_CH, n_requests, chunks), block(CONV_CH, CONV_TL);
 #define CONV_GO(TA, TW)                                                                                          \
   return launch_k(causal_conv_kernel<TA, TW>, grid, block, 0, stream, (const TA*)x, x_stride, (const TW*)w,      \
                   (const TW*)bias, (TA*)state, state_slot_stride, (TA*)out, out_stride, q_start, slots, channels, \

@@ -91,7 +91,8 @@ def core():
         lib.ie_gemm_simt_batched.argtypes = [P, I, P, I, P, I, I, I, I, I, I, I, I, L, L, L, P]
         lib.ie_cast_rows.argtypes = [P, P, I, I, I, P]
         lib.ie_outnorm_accumulate.argtypes = [P, P, I, I, P, I, P, I, I, I, F, P]
-        lib.ie_causal_conv.argtypes = [P, I, P, P, I, P, L, P, I, P, P, I, I, I, I, I, I, P]
+        lib.ie_causal_conv.argtypes = [P, I, P, P, I, P, L, P, I, P, P, I, I, I, I, I, I, I, P]
+        lib.ie_attention_rows.argtypes = [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, I, P, I, P, I, I, F, P]
         lib.ie_linear_recurrence.argtypes = [P, I, P, I, P, P, I, P, P, P, I, P, P, I, P, P, I, I, F, F, I, I, P]
         lib.ie_rownorm_rotate_write.argtypes = [P, P, P, I, I, I, P, P, P, P, P, I, F, P, I, P, P, P, P, I, I, I, I, I, I, I, P]
         lib.ie_moe_route.argtypes = [P, I, P, I, P, P, P, I, I, I, I, I, F, F, I, P]
@@ -107,7 +108,7 @@ def core():
                      "ie_layernorm", "ie_embed_bigram", "ie_add_bias", "ie_tanh", "ie_polynorm",
                      "ie_headnorm_kv_write", "ie_gemm_simt_batched", "ie_cast_rows", "ie_outnorm_accumulate",
                      "ie_causal_conv", "ie_linear_recurrence", "ie_rownorm_rotate_write", "ie_moe_route", "ie_moe_sort",
-                     "ie_moe_gemm", "ie_moe_combine"):
+                     "ie_moe_gemm", "ie_moe_combine", "ie_attention_rows"):
             getattr(lib, name).restype = c_int
         _core = lib
         _apply_check_limits()
@@ -284,6 +285,29 @@ def attention_general(q: torch.Tensor, out: torch.Tensor, kpool: torch.Tensor, v
            f"attention_general(head_dim={head_dim}, heads={n_heads}/{n_kv_heads})")
 
 
+def attention_rows(q: torch.Tensor, out: torch.Tensor, kpool: torch.Tensor, vpool: torch.Tensor, block_table: torch.Tensor,
+                   q_start: torch.Tensor, ctx_before: torch.Tensor, n_requests: int, max_rows: int, n_heads: int,
+                   n_kv_heads: int, head_dim: int, page_size: int, window: int | None, scale: float,
+                   score_bias: torch.Tensor | None = None, head_scale: torch.Tensor | None = None,
+                   v_head_dim: int | None = None, keep_first: int = 0, out_scale: float = 1.0) -> None:
+    """``attention_general`` for the requests of the step that bring at most ``max_rows`` (token, head-in-group) rows
+    (decode tokens, as a rule): a block per (token, query head) whose warps split the visible keys.  Rows of requests
+    that bring more are left untouched (the tile kernel's, with a work list of those requests)."""
+    assert q.stride(1) == 1 and out.stride(1) == 1 and kpool.dtype == q.dtype == out.dtype
+    assert block_table.dtype == torch.int32 and block_table.stride(1) == 1
+    if score_bias is not None:
+        assert score_bias.dtype is torch.float32 and score_bias.is_contiguous() and score_bias.shape[0] == n_heads
+    if head_scale is not None:
+        assert head_scale.dtype is torch.float32 and head_scale.is_contiguous() and head_scale.shape == (n_heads,)
+    _check(core().ie_attention_rows(_ptr(q), _ptr(out), _ptr(kpool), _ptr(vpool), _ptr(block_table), _ptr(q_start),
+                                    _ptr(ctx_before), q.stride(0), out.stride(0), block_table.stride(0), q.shape[0],
+                                    n_requests, int(max_rows), n_heads, n_kv_heads, head_dim, page_size, int(window or 0),
+                                    float(scale), dtype_code(q.dtype), _ptr(score_bias),
+                                    score_bias.shape[1] if score_bias is not None else 0, _ptr(head_scale),
+                                    int(v_head_dim or head_dim), int(keep_first or 0), float(out_scale), _stream()),
+           f"attention_rows(head_dim={head_dim}, heads={n_heads}/{n_kv_heads})")
+
+
 # -------------------------------------------------------------------------- gemm
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     """out[M,N] = a[M,K] @ w[N,K]^T in float32 arithmetic."""
@@ -334,10 +358,11 @@ CONV_MAX_TAPS = 16
 
 def causal_conv(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None, state: torch.Tensor, out: torch.Tensor,
                 q_start: torch.Tensor, slots: torch.Tensor, n_requests: int, activation: str | None = None,
-                write_state: bool = True) -> None:
+                write_state: bool = True, max_q_len: int | None = None) -> None:
     """A causal convolution per channel over each request's tokens of the step: ``out[t, c] = act(bias[c] + sum_j
     weight[c, j] * x[t - (taps - 1 - j), c])``.  ``state`` [slots, taps - 1, channels] (activation type) holds every
-    request's last inputs, oldest first, and is moved on by the step's tokens (with ``write_state``)."""
+    request's last inputs, oldest first, and is moved on by the step's tokens (with ``write_state``).  ``max_q_len``: the
+    most tokens one request brings (the launch is cut for it; the step's token count when not given)."""
     n, channels = x.shape
     taps = weight.shape[1]
     assert weight.shape == (channels, taps) and weight.is_contiguous() and x.stride(1) == 1 and out.stride(1) == 1
@@ -348,7 +373,8 @@ def causal_conv(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None
     _check(core().ie_causal_conv(_ptr(x), x.stride(0), _ptr(weight), _ptr(bias), dtype_code(weight.dtype), _ptr(state),
                                  state.stride(0), _ptr(out), out.stride(0), _ptr(q_start), _ptr(slots), n_requests,
                                  channels, taps, {None: 0, "silu": 1}[activation], 1 if write_state else 0,
-                                 dtype_code(x.dtype), _stream()), f"causal_conv(channels={channels}, taps={taps})")
+                                 dtype_code(x.dtype), int(max_q_len) if max_q_len else max(n, 1), _stream()),
+           f"causal_conv(channels={channels}, taps={taps})")
 
 
 def linear_recurrence(u: torch.Tensor, y_pre: torch.Tensor, r_pre: torch.Tensor, i_pre: torch.Tensor,
@@ -511,6 +537,8 @@ def attention_mma_library(head_dim: int, biased: bool = False):
         P, I, F = c_void_p, c_int, c_float
         lib.ie_attention_prefill_biased.argtypes = [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, I, P, P]
         lib.ie_attention_prefill_biased.restype = c_int
+        lib.ie_attention_prefill_kept.argtypes = [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P, I, P, I, F, P]
+        lib.ie_attention_prefill_kept.restype = c_int
         lib.ie_attention_decode_biased.argtypes = [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, I, P, I, P, P]
         lib.ie_attention_decode_biased.restype = c_int
         lib.ie_attention_prefill.argtypes = [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, I, P]
@@ -531,12 +559,25 @@ def attention_mma_library(head_dim: int, biased: bool = False):
 
 def attention_prefill_mma(q, out, kpool, vpool, block_table, q_start, ctx_before, work_req, work_pair0, n_work,
                           n_heads, n_kv_heads, head_dim, page_size, window, scale, rows: int = 64,
-                          score_bias_log2e=None, head_scale=None) -> None:
+                          score_bias_log2e=None, head_scale=None, keep_first: int = 0, out_scale: float = 1.0,
+                          float32_scores: bool = False) -> None:
     """Causal paged attention for any mix of portions and single tokens; bfloat16; the work list cuts each
     request's (token, head-in-group) pairs into tiles of ``rows`` (64 or 128).  With ``score_bias_log2e`` (float32
     [n_heads, D]: the bias by distance times log2 e, last column for every larger distance) or ``head_scale``
     (float32 [n_heads]) the bias build of the kernel runs."""
     assert q.dtype is torch.bfloat16 and q.stride(1) == 1 and out.stride(1) == 1
+    if keep_first or out_scale != 1.0 or float32_scores:
+        # the bias build (float32 scores, weights to two bfloat16 terms) also knows kept first keys beside the window
+        # and a multiplier of the output
+        dists = _score_extras(score_bias_log2e, head_scale, n_heads)
+        lib = attention_mma_library(head_dim, biased=True)
+        _check(lib.ie_attention_prefill_kept(_ptr(q), _ptr(out), _ptr(kpool), _ptr(vpool), _ptr(block_table),
+                                             _ptr(q_start), _ptr(ctx_before), _ptr(work_req), _ptr(work_pair0),
+                                             q.stride(0), out.stride(0), block_table.stride(0), n_work, n_heads,
+                                             n_kv_heads, head_dim, page_size, int(window or 0), float(scale), rows,
+                                             _ptr(score_bias_log2e), dists, _ptr(head_scale), int(keep_first or 0),
+                                             float(out_scale), _stream()), "attention_prefill_mma (bias build, kept keys)")
+        return
     if score_bias_log2e is not None or head_scale is not None:
         dists = _score_extras(score_bias_log2e, head_scale, n_heads)
         lib = attention_mma_library(head_dim, biased=True)

@@ -99,7 +99,7 @@ class GatedDeltaMixer:
         proj = self.proj(x, rt.ws.take("gated_delta_proj", (n, self.proj_width), rt.act_dtype))
         conv = rt.ws.take("gated_delta_conv", (n, self.conv_width), rt.act_dtype)
         kernels.causal_conv(proj[:, :self.conv_width], self.conv_weight, None, conv_state.state, conv, ctx.q_start,
-                            ctx.slots, ctx.n_requests, activation="silu", write_state=cache.write)
+                            ctx.slots, ctx.n_requests, activation="silu", write_state=cache.write, max_q_len=ctx.max_q_len)
         c0 = self.conv_width
         gate = proj[:, c0:c0 + self.vw]
         b_pre = proj[:, c0 + self.vw:c0 + self.vw + s.n_heads]

@@ -86,7 +86,7 @@ class GatedLinearRecurrence:
         proj = self.proj(x, rt.ws.take("recurrence_proj", (n, 2 * w), rt.act_dtype))
         u = rt.ws.take("recurrence_u", (n, w), rt.act_dtype)
         kernels.causal_conv(proj[:, w:], self.conv_weight, self.conv_bias, conv_state.state, u, ctx.q_start, ctx.slots,
-                            ctx.n_requests, activation=None, write_state=cache.write)
+                            ctx.n_requests, activation=None, write_state=cache.write, max_q_len=ctx.max_q_len)
         gates = rt.ws.take("recurrence_gates", (n, 2 * w), torch.float32)
         kernels.gemm_simt_batched(u, self.a_gate, gates[:, :w])
         kernels.gemm_simt_batched(u, self.i_gate, gates[:, w:])

@@ -312,7 +312,7 @@ def test_rownorm_rotate_write_kernel(dtype, hd, hdv, rot):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("decode", [False, True])
+@pytest.mark.parametrize("decode", [False, "tiles", "rows"])
 def test_a_key_stands_out_only_where_the_window_and_the_kept_tokens_allow(dtype, decode):
     """One key is made to stand out (its key and the last query share a large component); the last query must return
     that key's value when the key is the last one inside the window, the last kept first token, or at a page border
@@ -353,7 +353,10 @@ def test_a_key_stands_out_only_where_the_window_and_the_kept_tokens_allow(dtype,
                 vpool[order[p]] = float("nan")
         out = torch.empty(T, H * hdv, device=DEV, dtype=act)
         table_dev = dev_i32([table]).view(1, n_pages)
-        if decode:
+        if decode == "rows":        # the kernel of decode steps: a block per (token, head), the keys split over its warps
+            k().attention_rows(qd[T - 1:], out[T - 1:], kpool, vpool, table_dev, dev_i32([0, 1]), dev_i32([T - 1]), 1, 16,
+                               H, G, hd, ps, window, scale, None, None, hdv, keep, 0.7)
+        elif decode:
             k().attention_general(qd[T - 1:], out[T - 1:], kpool, vpool, table_dev, dev_i32([0, 1]), dev_i32([T - 1]),
                                   dev_i32([0]), dev_i32([0]), 1, H, G, hd, ps, window, scale, None, None, hdv, keep, 0.7)
         else:
