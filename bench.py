@@ -819,6 +819,42 @@ def run_family(args):
         return rows
 
     sizes = {}
+    if args.family == "kipezen" and args.family_step:
+        # one step launched kernel by kernel (no graphs) between cudaProfilerStart / Stop, for a launch list:
+        #   ncu --metrics gpu__time_duration.sum --clock-control none --profile-from-start off --csv --log-file L \
+        #       python bench.py --family kipezen --family-sizes w2048 --family-step decode
+        import tempfile
+        from inf_engine_b200 import ModelRunner
+        from inf_engine_b200.weights import write_random_model
+        size = (args.family_sizes or "w2048").split(",")[0]
+        kpz, _ = _kipezen_configs(size)
+        with tempfile.TemporaryDirectory() as tmp:
+            write_random_model(kpz, args.seed, tmp)
+            r = ModelRunner.from_dir(tmp, dtype="bfloat16", page_size=PAGE, n_pages=(args.batch + 1) * POOL_CONTEXT // PAGE,
+                                     max_requests=max(16, args.batch), use_graphs=False)
+        V = r.spec.vocab_size
+        rids = [f"d{i}" for i in range(args.batch)]
+        for rid in rids:
+            r.open(rid)
+        for i in range(0, args.batch, 4):
+            r.step([StepEntry(x, rng.integers(0, V, PROMPT_LEN).tolist(), []) for x in rids[i:i + 4]])
+        for _ in range(2):
+            r.step([StepEntry(x, [5], [0]) for x in rids])
+        r.open("p")
+        r.step([StepEntry("p", rng.integers(0, V, PROMPT_LEN).tolist(), [PROMPT_LEN - 1])])
+        r.close("p")
+        torch.cuda.synchronize()
+        torch.cuda.cudart().cudaProfilerStart()
+        if args.family_step == "decode":
+            r.step([StepEntry(x, [7], [0]) for x in rids])
+        else:
+            r.open("p")
+            r.step([StepEntry("p", rng.integers(0, V, PROMPT_LEN).tolist(), [PROMPT_LEN - 1])])
+        torch.cuda.synchronize()
+        torch.cuda.cudart().cudaProfilerStop()
+        clocks.stop()
+        print(json.dumps({"impl": "ours", "family": "kipezen", "step": args.family_step, "size": size, "launches": kernels.LAUNCHES}))
+        return 0
     if args.family == "kipezen":
         for size in (args.family_sizes.split(",") if args.family_sizes else list(FAMILY_SIZES)):
             kpz, brx = _kipezen_configs(size)
@@ -1040,6 +1076,8 @@ def main():
                     help="instead of the default workload: prefill and decode of another model family (barerax, kipezen) at sizes like "
                          "a real model's layers, beside a Llama model of equal size, and its kernels beside the like ones")
     ap.add_argument("--family-sizes", default=None, help="comma-separated subset of the family's sizes (w1024,w2048)")
+    ap.add_argument("--family-step", default=None, choices=["decode", "prefill"],
+                    help="with --family kipezen: run one such step kernel by kernel between cudaProfilerStart/Stop (for a launch list) and exit")
     ap.add_argument("--workload", default=None, metavar="N:MIN:MAX:NEW[:TEMP]",
                     help="instead of the step measurements: N requests through Engine.run_offline (continuous batching)")
     args = ap.parse_args()

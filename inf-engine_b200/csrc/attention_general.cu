@@ -250,18 +250,47 @@ extern "C" int ie_attention_general(const void* q, void* out, const void* kpool,
 // ------------------------------------------------------------------ few rows a request (decode steps)
 // The tile kernel above gives a (request, kv head) one block, which for a request that brings a single token walks
 // all its keys alone.  This one gives every (token, query head) of a request that brings at most `max_rows` (token,
-// head-in-group) rows a block of eight warps: warp w takes the visible keys w, w + 8, ... (the kept first keys, then
-// the window's), a key at a time with the head's dimensions spread over the lanes, four keys' loads in flight; each
-// warp keeps its own running maximum, sum and output, and the eight are merged in shared memory in warp order.  Same
-// arithmetic as above (float32 scores, weights and sums), same options.  Requests with more rows are left to the tile
-// kernel, whose work list then names only those.
-#define AR_WARPS 8
+// head-in-group) rows a block of sixteen warps.  A warp takes the visible keys (the kept first keys, then the window's)
+// 32 at a time, warp w the groups w, w + 16, ...: each lane forms the score of ONE key (the query is read from shared
+// memory, the key's row in 16-byte pieces where the sizes allow), the 32 scores meet the running maximum and sum
+// through two warp reductions, and then the lanes turn to the output's dimensions and add the 32 values' rows, the
+// weights passed round by shuffles, 16, 8 or 4 rows on their way together (the kernel is built for 2, 4 and 8 values
+// a lane: value heads up to 64, 128, 256).  The warps' results are merged in shared memory in warp order.  Same
+// arithmetic as above (float32 scores, weights and sums), same options.  Requests with more rows are left to the
+// tile kernel, whose work list then names only those.
+#define AR_WARPS 16
 #define AR_MAX_PER_LANE 8   // head sizes up to 256
 
 template <typename T>
+__device__ __forceinline__ float key_dot(const T* __restrict__ krow, const float* __restrict__ qs, int hd) {
+  float s0 = 0.f, s1 = 0.f;
+  if (sizeof(T) == 2 && (hd & 7) == 0 && (((uintptr_t)krow) & 15) == 0) {
+    for (int d = 0; d < hd; d += 8) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(krow + d);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+      const float4 qa = *reinterpret_cast<const float4*>(qs + d), qb = *reinterpret_cast<const float4*>(qs + d + 4);
+      const float2 k0 = __bfloat1622float2(h[0]), k1 = __bfloat1622float2(h[1]), k2 = __bfloat1622float2(h[2]),
+                   k3 = __bfloat1622float2(h[3]);
+      s0 = fmaf(qa.x, k0.x, s0); s1 = fmaf(qa.y, k0.y, s1); s0 = fmaf(qa.z, k1.x, s0); s1 = fmaf(qa.w, k1.y, s1);
+      s0 = fmaf(qb.x, k2.x, s0); s1 = fmaf(qb.y, k2.y, s1); s0 = fmaf(qb.z, k3.x, s0); s1 = fmaf(qb.w, k3.y, s1);
+    }
+  } else if (sizeof(T) == 4 && (hd & 3) == 0 && (((uintptr_t)krow) & 15) == 0) {
+    for (int d = 0; d < hd; d += 4) {
+      const float4 kv = *reinterpret_cast<const float4*>(krow + d);
+      const float4 qa = *reinterpret_cast<const float4*>(qs + d);
+      s0 = fmaf(qa.x, kv.x, s0); s1 = fmaf(qa.y, kv.y, s1); s0 = fmaf(qa.z, kv.z, s0); s1 = fmaf(qa.w, kv.w, s1);
+    }
+  } else {
+    for (int d = 0; d < hd; ++d) s0 = fmaf(qs[d], to_f32(krow[d]), s0);
+  }
+  return s0 + s1;
+}
+
+template <typename T, int PL>
 __global__ void __launch_bounds__(AR_WARPS * 32) attention_rows_kernel(AttnGeneralParams p, int n_requests, int max_rows) {
+  constexpr int VU = 32 / PL;                      // value rows in flight
   __shared__ float s_m[AR_WARPS], s_l[AR_WARPS];
-  extern __shared__ float s_acc[];                 // [AR_WARPS][hd_v]
+  extern __shared__ __align__(16) float s_dyn[];   // the query [hd rounded up to 4], then [AR_WARPS][hd_v]
   pdl_trigger();
   pdl_wait();
   const int n = blockIdx.x, head = blockIdx.y;
@@ -275,6 +304,8 @@ __global__ void __launch_bounds__(AR_WARPS * 32) attention_rows_kernel(AttnGener
   const int q0 = p.q_start[r_id], q_len = p.q_start[r_id + 1] - q0;
   if (q_len * group > max_rows) return;            // the tile kernel's
   const int hd = p.hd, hdv = p.hd_v;
+  float* qs = s_dyn;
+  float* s_acc = s_dyn + ((hd + 3) & ~3);
   const int c = head / group;
   const int limit = p.ctx_before[r_id] + (n - q0);                       // last visible key
   const int first = p.window > 0 ? max(0, limit - p.window + 1) : 0;
@@ -285,62 +316,57 @@ __global__ void __launch_bounds__(AR_WARPS * 32) attention_rows_kernel(AttnGener
   const T* vpool = (const T*)p.vpool;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const T* qrow = (const T*)p.q + (size_t)n * p.q_stride + head * hd;
-  float qv[AR_MAX_PER_LANE], acc[AR_MAX_PER_LANE];
+  for (int d = threadIdx.x; d < hd; d += AR_WARPS * 32) qs[d] = to_f32(qrow[d]);
+  __syncthreads();
+  float acc[PL];
 #pragma unroll
-  for (int j = 0; j < AR_MAX_PER_LANE; ++j) {
-    const int d = lane + 32 * j;
-    qv[j] = d < hd ? to_f32(qrow[d]) : 0.f;
-    acc[j] = 0.f;
-  }
+  for (int j = 0; j < PL; ++j) acc[j] = 0.f;
   const float my_scale = p.head_scale != nullptr ? p.scale * p.head_scale[head] : p.scale;
   const float* my_bias = p.score_bias != nullptr ? p.score_bias + (size_t)head * p.bias_dists : nullptr;
   float m_run = -INFINITY, l_run = 0.f;
-  for (int i0 = warp; i0 < n_vis; i0 += 4 * AR_WARPS) {
-    float part[4], vv[4][AR_MAX_PER_LANE];          // the values are fetched with the keys: one memory latency a round
-    int kpos[4];
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int idx = i0 + u * AR_WARPS;
-      part[u] = 0.f;
-      kpos[u] = -1;
-      if (idx < n_vis) {
-        const int kp = idx < n_keep ? idx : first + (idx - n_keep);
-        const int page = IE_PAGE(table[kp / p.page_size]);
-        if (page >= 0) {
-          kpos[u] = kp;
-          const size_t at = ((size_t)page * p.n_kv_heads + c) * p.page_size + (kp % p.page_size);
-          const T* krow = kpool + at * hd;
-          const T* vrow = vpool + at * hdv;
-          T kraw[AR_MAX_PER_LANE], vraw[AR_MAX_PER_LANE];
-#pragma unroll
-          for (int j = 0; j < AR_MAX_PER_LANE; ++j) {
-            const int d = lane + 32 * j;
-            if (d < hd) kraw[j] = krow[d];
-            if (d < hdv) vraw[j] = vrow[d];
-          }
-#pragma unroll
-          for (int j = 0; j < AR_MAX_PER_LANE; ++j) {
-            const int d = lane + 32 * j;
-            if (d < hd) part[u] = fmaf(qv[j], to_f32(kraw[j]), part[u]);
-            vv[u][j] = d < hdv ? to_f32(vraw[j]) : 0.f;
-          }
-        }
+  for (int i0 = warp * 32; i0 < n_vis; i0 += AR_WARPS * 32) {
+    const int idx = i0 + lane;
+    float sc = -INFINITY;
+    long long at = -1;                             // this lane's key: its row in the pools
+    if (idx < n_vis) {
+      const int kp = idx < n_keep ? idx : first + (idx - n_keep);
+      const int page = IE_PAGE(table[kp / p.page_size]);
+      if (page >= 0) {
+        at = ((long long)page * p.n_kv_heads + c) * p.page_size + (kp % p.page_size);
+        sc = key_dot(kpool + at * hd, qs, hd) * my_scale;
+        if (my_bias != nullptr) sc += my_bias[min(limit - kp, p.bias_dists - 1)];
       }
     }
+    const float m_new = fmaxf(m_run, warp_max(sc));
+    if (m_new == -INFINITY) continue;              // (the same in every lane)
+    const float alpha = expf(m_run - m_new);       // exp(-inf) = 0 the first time
+    const float e = at >= 0 ? expf(sc - m_new) : 0.f;
+    l_run = l_run * alpha + warp_sum(e);
+    m_run = m_new;
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      if (kpos[u] < 0) continue;                   // (the same in every lane of the warp)
-      float sc = warp_sum(part[u]) * my_scale;
-      if (my_bias != nullptr) sc += my_bias[min(limit - kpos[u], p.bias_dists - 1)];
-      const float m_new = fmaxf(m_run, sc);
-      const float alpha = expf(m_run - m_new), e = expf(sc - m_new);
-      l_run = l_run * alpha + e;
-      m_run = m_new;
+    for (int j = 0; j < PL; ++j) acc[j] *= alpha;
+    const int n_here = min(32, n_vis - i0);
+    for (int kk0 = 0; kk0 < n_here; kk0 += VU) {    // VU keys' value rows on their way together
+      float w[VU];
+      T vals[VU][PL];
 #pragma unroll
-      for (int j = 0; j < AR_MAX_PER_LANE; ++j) {
-        const int d = lane + 32 * j;
-        if (d < hdv) acc[j] = fmaf(e, vv[u][j], acc[j] * alpha);
+      for (int u = 0; u < VU; ++u) {
+        const int kk = (kk0 + u) & 31;
+        const float wk = __shfl_sync(0xffffffffu, e, kk);
+        const long long vat = __shfl_sync(0xffffffffu, at, kk);
+        const bool live = kk0 + u < n_here && vat >= 0;
+        w[u] = live ? wk : 0.f;
+        const T* vrow = vpool + (live ? vat : 0) * hdv;
+#pragma unroll
+        for (int j = 0; j < PL; ++j) {
+          const int d = lane + 32 * j;
+          vals[u][j] = (d < hdv && live) ? vrow[d] : from_f32<T>(0.f);
+        }
       }
+#pragma unroll
+      for (int u = 0; u < VU; ++u)
+#pragma unroll
+        for (int j = 0; j < PL; ++j) acc[j] = fmaf(w[u], to_f32(vals[u][j]), acc[j]);
     }
   }
   if (lane == 0) {
@@ -348,7 +374,7 @@ __global__ void __launch_bounds__(AR_WARPS * 32) attention_rows_kernel(AttnGener
     s_l[warp] = l_run;
   }
 #pragma unroll
-  for (int j = 0; j < AR_MAX_PER_LANE; ++j) {
+  for (int j = 0; j < PL; ++j) {
     const int d = lane + 32 * j;
     if (d < hdv) s_acc[warp * hdv + d] = acc[j];
   }
@@ -388,10 +414,21 @@ extern "C" int ie_attention_rows(const void* q, void* out, const void* kpool, co
   p.n_work = 0; p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.hd = hd; p.page_size = page_size;
   p.window = window; p.scale = scale; p.score_bias = score_bias; p.bias_dists = bias_dists;
   p.head_scale = head_scale; p.hd_v = hd_v; p.keep_first = keep_first > 0 ? keep_first : 0; p.out_scale = out_scale;
-  const size_t smem = sizeof(float) * AR_WARPS * (size_t)hd_v;
+  const size_t smem = sizeof(float) * (((size_t)hd + 3) / 4 * 4 + AR_WARPS * (size_t)hd_v);
   dim3 grid(n_tokens, n_heads);
-  if (act_dtype == IE_F32) return launch_k(attention_rows_kernel<float>, grid, AR_WARPS * 32, smem, stream, p, n_requests, max_rows);
-  if (act_dtype == IE_BF16) return launch_k(attention_rows_kernel<bf16>, grid, AR_WARPS * 32, smem, stream, p, n_requests, max_rows);
+  const int pl = hd_v <= 64 ? 2 : (hd_v <= 128 ? 4 : 8);
+#define AR_GO(T, PL) return launch_k(attention_rows_kernel<T, PL>, grid, AR_WARPS * 32, smem, stream, p, n_requests, max_rows)
+  if (act_dtype == IE_F32) {
+    if (pl == 2) AR_GO(float, 2);
+    if (pl == 4) AR_GO(float, 4);
+    AR_GO(float, 8);
+  }
+  if (act_dtype == IE_BF16) {
+    if (pl == 2) AR_GO(bf16, 2);
+    if (pl == 4) AR_GO(bf16, 4);
+    AR_GO(bf16, 8);
+  }
+#undef AR_GO
   return IE_BAD_DTYPE;
 }
 

@@ -12,8 +12,9 @@
 // DK and DV are compile-time constants (-DIE_GD_DK, -DIE_GD_DV): a library is built per pair when a model first asks.
 // A block owns one (request, head).  Column j of S (value channel j) belongs to KS neighbouring threads, each with
 // DK / KS of its rows in registers, so S^T k, the update and S^T q are sums inside a thread and a shuffle among
-// those lanes.  The step's tokens of the request are walked in tiles of TT: (A) the tile's q, k, v and gate go to
-// shared memory as float32, a thread per token forms beta and g and a warp per token makes q and k unit vectors;
+// those lanes.  The step's tokens of the request are walked in tiles of TT, whose q, k, v and gate are fetched into
+// registers while the tile before is being run: (A) they go to shared memory as float32, a thread per token forms
+// beta and g and a warp per token makes q and k unit vectors;
 // (B) every thread runs the tile's tokens in order; (C) a warp per token norms and gates the outputs.  The order
 // of every sum is fixed by the token and the channel alone, so a token's result does not depend on how the
 // sequence was cut into steps or on what else the step holds.  A decode step is a tile of one token.
@@ -70,6 +71,21 @@ struct GatedDeltaParams {
   int write_state;
 };
 
+// Loads of a tile's inputs that stay where they are written (volatile): they are issued before the tile ahead is run
+// and used after it; left to itself the compiler moves them down to their use and the tile then waits for memory.
+__device__ __forceinline__ float gd_ld_early(const float* p) {
+  float v;
+  asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ float gd_ld_early(const bf16* p) {
+  unsigned short v;
+  asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(v) : "l"(p));
+  return __uint_as_float((unsigned)v << 16);
+}
+#define GD_PQ ((GD_TT * GD_DK + GD_THREADS - 1) / GD_THREADS)   // elements of a tile's q (and k) a thread fetches
+#define GD_PV ((GD_TT * GD_DV + GD_THREADS - 1) / GD_THREADS)   // of its v (and gate)
+
 __device__ __forceinline__ int gd_place(int i) { return (i / GD_DKP) * GD_LD + (i % GD_DKP); }   // channel -> place
 __device__ __forceinline__ float gd_column_sum(float v) {
 #pragma unroll
@@ -112,20 +128,51 @@ __global__ void __launch_bounds__(GD_THREADS) gated_delta_kernel(GatedDeltaParam
 #pragma unroll
   for (int i = 0; i < GD_DKP; ++i) S[i] = active ? st[(size_t)(row0 + i) * GD_DV + j] : 0.f;
 
+  // a tile's inputs in registers, fetched while the tile ahead is being run
+  float fq[GD_PQ], fk[GD_PQ], fv[GD_PV], fg[GD_PV];
+  auto fetch = [&](int t0, int nt) {
+#pragma unroll
+    for (int u = 0; u < GD_PQ; ++u) {
+      const int e = tid + u * GD_THREADS;
+      const int tt = e / GD_DK, i = e - tt * GD_DK;
+      if (tt < nt) {
+        const size_t row = (size_t)(t0 + tt) * p.qk_stride + i;
+        fq[u] = gd_ld_early(Q + row);
+        fk[u] = gd_ld_early(K + row);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < GD_PV; ++u) {
+      const int e = tid + u * GD_THREADS;
+      const int tt = e / GD_DV, i = e - tt * GD_DV;
+      if (tt < nt) {
+        fv[u] = gd_ld_early(V + (size_t)(t0 + tt) * p.v_stride + i);
+        fg[u] = gd_ld_early(G + (size_t)(t0 + tt) * p.gate_stride + i);
+      }
+    }
+  };
+  if (q0 < q1) fetch(q0, min(GD_TT, q1 - q0));
+
   for (int t0 = q0; t0 < q1; t0 += GD_TT) {
     const int nt = min(GD_TT, q1 - t0);
     // (A) the tile's vectors, the two numbers of every token, the unit vectors
-    for (int e = tid; e < nt * GD_DK; e += GD_THREADS) {
+#pragma unroll
+    for (int u = 0; u < GD_PQ; ++u) {
+      const int e = tid + u * GD_THREADS;
       const int tt = e / GD_DK, i = e - tt * GD_DK;
-      const size_t row = (size_t)(t0 + tt) * p.qk_stride + i;
-      sq[tt][gd_place(i)] = to_f32(Q[row]);
-      sk[tt][gd_place(i)] = to_f32(K[row]);
+      if (tt < nt) {
+        sq[tt][gd_place(i)] = fq[u];
+        sk[tt][gd_place(i)] = fk[u];
+      }
     }
-    for (int e = tid; e < nt * GD_DV; e += GD_THREADS) {
+#pragma unroll
+    for (int u = 0; u < GD_PV; ++u) {
+      const int e = tid + u * GD_THREADS;
       const int tt = e / GD_DV, i = e - tt * GD_DV;
-      sv[tt][i] = to_f32(V[(size_t)(t0 + tt) * p.v_stride + i]);
-      const float gt = to_f32(G[(size_t)(t0 + tt) * p.gate_stride + i]);
-      sg[tt][i] = to_f32(gain[i]) * (gt / (1.f + expf(-gt)));
+      if (tt < nt) {
+        sv[tt][i] = fv[u];
+        sg[tt][i] = to_f32(gain[i]) * (fg[u] / (1.f + expf(-fg[u])));
+      }
     }
     if (tid < nt) {
       const float b = to_f32(((const TA*)p.b_pre)[(size_t)(t0 + tid) * p.ba_stride + h]);
@@ -152,6 +199,7 @@ __global__ void __launch_bounds__(GD_THREADS) gated_delta_kernel(GatedDeltaParam
       }
     }
     __syncthreads();
+    if (t0 + GD_TT < q1) fetch(t0 + GD_TT, min(GD_TT, q1 - t0 - GD_TT));     // lands while this tile runs
     // (B) the tile's tokens in order; this thread's rows of its column of the state
 #pragma unroll 2
     for (int tt = 0; tt < nt; ++tt) {

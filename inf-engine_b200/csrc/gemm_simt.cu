@@ -112,3 +112,55 @@ extern "C" int ie_gemm_simt_batched(const void* A, int a_dtype, const void* W, i
     default: return IE_BAD_DTYPE;
   }
 }
+
+// ------------------------------------------------------------------ few output columns (a router)
+// C[m, n] = sum_k A[m, k] W[n, k] for N of a few dozen: the tile kernel above would give all of it to one block
+// that walks K alone.  Here a block takes a row of A into shared memory and each of its eight warps takes outputs
+// n = warp, warp + 8, ...: the lanes stride k with four partial sums each, then a tree over the lanes.  The order is
+// fixed by (n, k) alone, so a row's result does not depend on how many rows share the launch.  float32 arithmetic.
+template <typename TA, typename TW>
+__global__ void __launch_bounds__(256) gemm_rowdot_kernel(const TA* __restrict__ A, const TW* __restrict__ W,
+                                                          float* __restrict__ C, int N, int K, int lda, int ldw, int ldc) {
+  extern __shared__ float a_s[];
+  pdl_trigger();
+  pdl_wait();
+  const int m = blockIdx.x;
+  for (int k = threadIdx.x; k < K; k += blockDim.x) a_s[k] = to_f32(A[(size_t)m * lda + k]);
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int n = warp; n < N; n += 8) {
+    const TW* w = W + (size_t)n * ldw;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    int k = lane;
+    for (; k + 96 < K; k += 128) {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) acc[u] = fmaf(a_s[k + 32 * u], to_f32(w[k + 32 * u]), acc[u]);
+    }
+    for (int u = 0; k < K; k += 32, ++u) acc[u & 3] = fmaf(a_s[k], to_f32(w[k]), acc[u & 3]);
+    const float total = warp_sum((acc[0] + acc[1]) + (acc[2] + acc[3]));
+    if (lane == 0) C[(size_t)m * ldc + n] = total;
+  }
+}
+
+extern "C" int ie_gemm_rowdot(const void* A, int a_dtype, const void* W, int w_dtype, float* C, int M, int N, int K,
+                              int lda, int ldw, int ldc, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return IE_OK;
+  if (K <= 0 || (size_t)K * sizeof(float) > 200 * 1024) return IE_BAD_SIZE;
+  const size_t smem = (size_t)K * sizeof(float);
+#define RD_GO(TA, TW)                                                                                              \
+  {                                                                                                                \
+    if (smem > 47 * 1024) {                                                                                        \
+      cudaError_t e = cudaFuncSetAttribute(gemm_rowdot_kernel<TA, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                           (int)smem);                                                             \
+      if (e != cudaSuccess) return (int)e;                                                                         \
+    }                                                                                                              \
+    return launch_k(gemm_rowdot_kernel<TA, TW>, M, 256, smem, stream, (const TA*)A, (const TW*)W, C, N, K, lda, ldw, \
+                    ldc);                                                                                          \
+  }
+  if (a_dtype == IE_F32 && w_dtype == IE_F32) RD_GO(float, float);
+  if (a_dtype == IE_F32 && w_dtype == IE_BF16) RD_GO(float, bf16);
+  if (a_dtype == IE_BF16 && w_dtype == IE_F32) RD_GO(bf16, float);
+  if (a_dtype == IE_BF16 && w_dtype == IE_BF16) RD_GO(bf16, bf16);
+#undef RD_GO
+  return IE_BAD_DTYPE;
+}

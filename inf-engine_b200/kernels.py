@@ -89,6 +89,7 @@ def core():
         lib.ie_headnorm_kv_write.argtypes = [P, P, P, I, I, I, P, P, I, F, P, P, P, I, I, I, I, I, I, I, I, P]
         lib.ie_gemm_simt.argtypes = [P, I, P, I, P, I, I, I, I, I, I, I, P]
         lib.ie_gemm_simt_batched.argtypes = [P, I, P, I, P, I, I, I, I, I, I, I, I, L, L, L, P]
+        lib.ie_gemm_rowdot.argtypes = [P, I, P, I, P, I, I, I, I, I, I, P]
         lib.ie_cast_rows.argtypes = [P, P, I, I, I, P]
         lib.ie_outnorm_accumulate.argtypes = [P, P, I, I, P, I, P, I, I, I, F, P]
         lib.ie_causal_conv.argtypes = [P, I, P, P, I, P, L, P, I, P, P, I, I, I, I, I, I, I, P]
@@ -108,7 +109,7 @@ def core():
                      "ie_layernorm", "ie_embed_bigram", "ie_add_bias", "ie_tanh", "ie_polynorm",
                      "ie_headnorm_kv_write", "ie_gemm_simt_batched", "ie_cast_rows", "ie_outnorm_accumulate",
                      "ie_causal_conv", "ie_linear_recurrence", "ie_rownorm_rotate_write", "ie_moe_route", "ie_moe_sort",
-                     "ie_moe_gemm", "ie_moe_combine", "ie_attention_rows"):
+                     "ie_moe_gemm", "ie_moe_combine", "ie_attention_rows", "ie_gemm_rowdot"):
             getattr(lib, name).restype = c_int
         _core = lib
         _apply_check_limits()
@@ -318,6 +319,17 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
     _check(core().ie_gemm_simt(_ptr(a), dtype_code(a.dtype), _ptr(w), dtype_code(w.dtype), _ptr(out),
                                dtype_code(out.dtype), m, n, k, a.stride(0), w.stride(0), out.stride(0),
                                _stream()), f"gemm_simt({a.dtype},{w.dtype}->{out.dtype})")
+
+
+def gemm_rowdot(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M,N] = a[M,K] @ w[N,K]^T in float32 arithmetic for a few dozen outputs (a router): a block per row of ``a``, a
+    warp per output."""
+    m, k = a.shape
+    n = w.shape[0]
+    assert w.shape[1] == k and out.shape == (m, n) and out.dtype is torch.float32
+    assert a.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    _check(core().ie_gemm_rowdot(_ptr(a), dtype_code(a.dtype), _ptr(w), dtype_code(w.dtype), _ptr(out), m, n, k, a.stride(0),
+                                 w.stride(0), out.stride(0), _stream()), f"gemm_rowdot({a.dtype},{w.dtype})")
 
 
 def gemm_simt_batched(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:

@@ -72,7 +72,8 @@ class RoutedExperts:
         n, E, top = x.shape[0], s.n_experts, s.top
         n_pairs = n * top
         logits = ws.take("moe_logits", (n, self.router.shape[0]), torch.float32)
-        kernels.gemm_simt(x, self.router, logits)
+        # float32 products and sums whatever the activation type; few outputs: a warp per (token, expert)
+        (kernels.gemm_rowdot if self.router.shape[0] <= 128 else kernels.gemm_simt)(x, self.router, logits)
         ids = ws.take("moe_ids", (n, top), torch.int32)
         weights = ws.take("moe_weights", (n, top), torch.float32)
         gate = ws.take("moe_gate", (n,), torch.float32) if self.shared is not None else None
