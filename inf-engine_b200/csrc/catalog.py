@@ -16,6 +16,6 @@ def all_build_requests():
         reqs.append((f"attn_mma_hd{hd}_bias", ["attention_mma.cu"], {"IE_HD": hd, "IE_ATTN_BIAS": 1}, ["attention_noalloc.h"]))
     for d in (16, 24, 32, 48, 64, 128):  # head sizes of the delta-rule mixer worth having before a model asks
         reqs.append((f"delta_rule_d{d}", ["delta_rule.cu"], {"IE_DR_DIM": d}, []))
-    for dk, dv in ((32, 64), (64, 64), (128, 128)):   # (key, value) head sizes of the gated delta rule worth having early
+    for dk, dv in ((64, 64), (64, 128), (128, 128)):   # (key, value) head sizes of the gated delta rule worth having early
         reqs.append((f"gated_delta_k{dk}_v{dv}", ["gated_delta.cu"], {"IE_GD_DK": dk, "IE_GD_DV": dv}, []))
     return reqs

@@ -303,14 +303,17 @@ class PagedAttention:
             return
         # float32 arithmetic on CUDA cores: requests that bring at most 16 rows (decode tokens) get a block per (token,
         # head) whose warps split the keys; the others the tile kernel, with a work list of those requests only
-        n_small = ctx.n_requests if ctx.max_q_len * group <= 16 else ctx.keys_of_small_requests(group, 16)[0]
+        # (layers without the newer options keep the tile kernel for every request: all their cuts then walk the same
+        # key tiles and agree with each other to the last bits)
+        newer = self.row_mode or self.keep_first or self.out_scale != 1.0
+        n_small = 0 if not newer else (ctx.n_requests if ctx.max_q_len * group <= 16 else ctx.keys_of_small_requests(group, 16)[0])
         if n_small:
             kernels.attention_rows(q, out, cache.k, cache.v, kvctx.block_table, ctx.q_start, ctx.ctx_before,
                                    ctx.n_requests, 16, s.n_heads, s.n_kv_heads, s.head_dim, ctx.page_size, s.window,
                                    self.scale, bias, head_scale, self.v_dim, self.keep_first, self.out_scale)
             if n_small == ctx.n_requests:
                 return
-        if (self.rt.act_dtype is torch.bfloat16 and s.head_dim in kernels.MMA_HEAD_DIMS and self.v_dim == s.head_dim
+        if (newer and self.rt.act_dtype is torch.bfloat16 and s.head_dim in kernels.MMA_HEAD_DIMS and self.v_dim == s.head_dim
                 and group <= 16):
             # prompt portions of a layer with kept first keys, a multiplier of its output or scores that must be
             # float32: the tensor-core kernels' bias build (float32 scores, maxima and sums; weights to two bfloat16 terms)

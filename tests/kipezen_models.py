@@ -55,7 +55,7 @@ KPZ_B = _model(157, 96, 1e-6, [
 # heads of 64 with values of 64, five gate blocks, more kept tokens than a page of 8 holds, no rotation at all in
 # the second parallel layer and no window in it either (every key visible)
 KPZ_C = _model(300, 128, 1e-5, [
-    _par(2, 2, 64, 64, 0.125, (20000.0, 16), 33, 11, 80, 5, 4, 1.1, 0.9, _moe(48, 4, 2, 2, 2, 2.0, 16)),
+    _par(2, 2, 64, 64, 0.125, (30000.0, 16), 33, 11, 80, 5, 4, 1.1, 0.9, _moe(48, 4, 2, 2, 2, 2.0, 16)),
     _delta(2, 1, 64, 64, 4, _moe(16, 16, 2, 4, 1, 1.5, 48)),
     _par(2, 1, 32, 48, 0.18, None, None, 0, 64, 2, 3, 0.6, 0.6, None),
 ])

@@ -287,7 +287,7 @@ def test_rownorm_rotate_write_kernel(dtype, hd, hdv, rot):
     qb, kb, vb = torch.randn(H * hd).to(act), torch.randn(G * hd).to(act), torch.randn(G * hdv).to(act)
     qg, kg = (1.5 + torch.rand(H * hd)).to(act), (1.5 + torch.rand(G * hd)).to(act)
     pos = torch.tensor([0, 1, 7, 137, 4095, 1000003])
-    base = 20000.0
+    base = 50000.0
     wq = plain.rms_unit(q.double() + qb.double(), 1e-5) * qg.double()
     wk = plain.rms_unit(kk.double() + kb.double(), 1e-5) * kg.double()
     wq, wk = wq.view(n, H, hd), wk.view(n, G, hd)
